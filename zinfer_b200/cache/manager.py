@@ -13,7 +13,8 @@ layers only, and `conv_state [n_conv][K-1][D]` zeroed at reset (src/model.zig:14
   [layers of the group, pages, kv heads, page_size, width] (keys and values for attention; a
   mixer may ask for another width of the second, or for one tensor only) and one page table
   [slots, pages per sequence] shared by the group's layers.  A group with a window gives pages
-  back as soon as every position in them has left the window.
+  back as soon as every position in them has left the window; the pages that hold a sequence's first
+  `keep_first` tokens are never given back while the sequence lives.
 * a mixer that asks for fixed-size state gets a row per slot in a tensor
   [calls with that state shape, slots, *shape], zeroed when the slot is handed out.
 
@@ -86,7 +87,9 @@ class KVGroup:
         self.table_dev = torch.full((max_slots, max_pages_per_seq), -1, dtype=torch.int32, device=device)
         self.free_pages = list(range(num_pages - 1, -1, -1))      # pop() hands out page 0 first
         self.n_pages_of = np.zeros(max_slots, dtype=np.int64)     # logical pages a slot has reached
-        self.first_page_of = np.zeros(max_slots, dtype=np.int64)  # pages below it were given back
+        self.first_page_of = np.zeros(max_slots, dtype=np.int64)  # pages below it were given back ...
+        # ... except the first `kept_pages`, which hold tokens that every later query still sees
+        self.kept_pages = -(-request.keep_first // page_size) if request.window > 0 else 0
         self.dirty = False
 
     def pages_needed(self, slot: int, new_len: int) -> int:
@@ -108,14 +111,15 @@ class KVGroup:
         first_needed = max(0, length + 1 - w) // self.page_size
         while self.first_page_of[slot] < min(first_needed, self.n_pages_of[slot]):
             i = int(self.first_page_of[slot])
-            self.free_pages.append(int(self.table_host[slot, i]))
-            self.table_host[slot, i] = -1
+            if i >= self.kept_pages:
+                self.free_pages.append(int(self.table_host[slot, i]))
+                self.table_host[slot, i] = -1
+                self.dirty = True
             self.first_page_of[slot] += 1
-            self.dirty = True
 
     def release(self, slot: int) -> None:
-        for i in range(int(self.first_page_of[slot]), int(self.n_pages_of[slot])):
-            self.free_pages.append(int(self.table_host[slot, i]))
+        for p in self.pages_held(slot):
+            self.free_pages.append(p)
         if self.n_pages_of[slot]:
             self.table_host[slot, :self.n_pages_of[slot]] = -1
             self.dirty = True
@@ -123,7 +127,8 @@ class KVGroup:
         self.first_page_of[slot] = 0
 
     def pages_held(self, slot: int) -> list[int]:
-        return [int(p) for p in self.table_host[slot, int(self.first_page_of[slot]):int(self.n_pages_of[slot])]]
+        n, first = int(self.n_pages_of[slot]), int(self.first_page_of[slot])
+        return [int(self.table_host[slot, i]) for i in range(n) if i < self.kept_pages or i >= first]
 
     def sync(self) -> None:
         if self.dirty:
@@ -162,17 +167,20 @@ class CacheManager:
         # A reader may look further back than the call whose cache it reads (or not at all as far): the
         # storage keeps what the widest of them sees (window 0 = everything), each call masks for itself.
         keep: dict[int, int] = {}
+        first: dict[int, int] = {}      # the most first tokens any of them keeps beside its window
         for c, owner in self._kv_of_call.items():
             if owner != c:
                 if owner not in self._kv_of_call or self._kv_of_call[owner] != owner:
                     raise CacheError(f"call {c} reads the cache of call {owner}, which owns none")
-                if replace(calls[owner].kv, window=0) != replace(calls[c].kv, window=0):
+                if replace(calls[owner].kv, window=0, keep_first=0) != replace(calls[c].kv, window=0, keep_first=0):
                     raise CacheError(f"call {c} reads the cache of call {owner} but asks for a different layout")
             w = calls[c].kv.window
             keep[owner] = w if owner not in keep else (0 if w <= 0 or keep[owner] <= 0 else max(keep[owner], w))
+            first[owner] = max(first.get(owner, 0), calls[c].kv.keep_first)
         for c, owner in self._kv_of_call.items():
             if owner == c:
-                by_request.setdefault(replace(calls[c].kv, window=keep[c]), []).append(c)
+                by_request.setdefault(replace(calls[c].kv, window=keep[c], keep_first=first[c] if keep[c] > 0 else 0),
+                                      []).append(c)
         for request, owners in by_request.items():
             g = len(self.groups)
             self.groups.append(KVGroup(request, len(owners), self.num_pages, page_size, max_slots,

@@ -15,7 +15,7 @@
 #include "common.cuh"
 #include <math.h>
 
-#define ATT_MAX_HD 256
+#define ATT_MAX_HD 640
 #define ATT_ROWS 16      // query rows (token, head-in-group) per block
 #define ATT_TK 32        // keys per tile: one lane per key
 #define ATT_WARPS 4
@@ -258,36 +258,68 @@ __device__ __forceinline__ void span_norm_row(const T* __restrict__ row, int n, 
   }
 }
 
+// Element d of a row of heads (hd wide each) after the rotation of the first n_rot entries of every head, entry i
+// paired with entry i + n_rot/2; `buf` holds the row before the rotation.
+__device__ __forceinline__ float span_rotated(const float* __restrict__ buf, int d, int hd, int n_rot,
+                                              const float* __restrict__ inv_freq, int pos) {
+  const int e = d % hd;
+  if (e >= n_rot) return buf[d];
+  const int half = n_rot >> 1;
+  const float ang = (float)pos * inv_freq[e < half ? e : e - half];
+  const float c = cosf(ang), sn = sinf(ang);
+  return e < half ? buf[d] * c - buf[d + half] * sn : buf[d - half] * sn + buf[d] * c;
+}
+
 // Block (t, 0) prepares the token's queries, block (t, 1) its keys and values (absent when write_kv = 0).
+// With inv_freq the first n_rot entries of every q and k head are rotated by the token's position after the
+// norm (pairs (i, i + n_rot/2)); the normalised row then waits in shared memory (max(H, Hkv) * hd floats).
 template <typename T>
 __global__ void __launch_bounds__(SPAN_THREADS)
     qk_prepare_span_kernel(const T* __restrict__ qkv, int ld, T* __restrict__ q_out, T* __restrict__ k_cache,
                            T* __restrict__ v_cache, const float* __restrict__ q_w, const float* __restrict__ k_w,
                            const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                            const int* __restrict__ seq_slot, const int* __restrict__ page_table, int pt_stride, int H,
-                           int Hkv, int hd, int vd, float eps, int page_size, int* status) {
+                           int Hkv, int hd, int vd, float eps, int page_size, int* status,
+                           const float* __restrict__ inv_freq, int n_rot) {
   __shared__ float scratch[32];
+  extern __shared__ float span_row[];
   zk_let_next_start();
   zk_wait_prior();   // qkv is the kernel before's result
   const int t = blockIdx.x, tid = threadIdx.x;
   const int qd = H * hd, kd = Hkv * hd;
   const T* row = qkv + (size_t)t * ld;
+  const int pos = tok_pos[t];
   if (blockIdx.y == 0) {
     T* dst = q_out + (size_t)t * qd;
+    if (inv_freq) {
+      span_norm_row(row, qd, q_w, eps, scratch, [&](int d, float v) { span_row[d] = v; });
+      __syncthreads();
+      for (int d = tid; d < qd; d += SPAN_THREADS) dst[d] = from_f32<T>(span_rotated(span_row, d, hd, n_rot, inv_freq, pos));
+      return;
+    }
     span_norm_row(row, qd, q_w, eps, scratch, [&](int d, float v) { dst[d] = from_f32<T>(v); });
     return;
   }
-  const int pos = tok_pos[t];
   const int page = page_table[(size_t)seq_slot[tok_seq[t]] * pt_stride + pos / page_size];
   if (page < 0) {
     if (tid == 0) atomicExch(status, 2);
     return;
   }
   const int in_page = pos % page_size;
-  span_norm_row(row + qd, kd, k_w, eps, scratch, [&](int d, float v) {
-    const int kh = d / hd, e = d - kh * hd;
-    k_cache[(((size_t)page * Hkv + kh) * page_size + in_page) * hd + e] = from_f32<T>(v);
-  });
+  if (inv_freq) {
+    span_norm_row(row + qd, kd, k_w, eps, scratch, [&](int d, float v) { span_row[d] = v; });
+    __syncthreads();
+    for (int d = tid; d < kd; d += SPAN_THREADS) {
+      const int kh = d / hd, e = d - kh * hd;
+      k_cache[(((size_t)page * Hkv + kh) * page_size + in_page) * hd + e] =
+          from_f32<T>(span_rotated(span_row, d, hd, n_rot, inv_freq, pos));
+    }
+  } else {
+    span_norm_row(row + qd, kd, k_w, eps, scratch, [&](int d, float v) {
+      const int kh = d / hd, e = d - kh * hd;
+      k_cache[(((size_t)page * Hkv + kh) * page_size + in_page) * hd + e] = from_f32<T>(v);
+    });
+  }
   const T* vrow = row + qd + kd;
   for (int d = tid; d < Hkv * vd; d += SPAN_THREADS) {
     const int kh = d / vd, e = d - kh * vd;
@@ -308,7 +340,11 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
                     const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
                     const int* __restrict__ page_table, int pt_stride, int n_tokens, int H, int Hkv, int hd,
                     int page_size, int window, float scale, int bq, int gc, int num_splits, int split_keys, int vd,
-                    const float* __restrict__ bias_r1, const float* __restrict__ bias_r2, int cross) {
+                    const float* __restrict__ bias_r1, const float* __restrict__ bias_r2, int cross, int keep,
+                    const float* __restrict__ sink, int v_from_k) {
+  // keep: with a window, the first `keep` positions of a sequence stay visible to every later query.
+  // sink [H]: exp(sink_h) is one more term of head h's softmax denominator (no key, no value, unscaled).
+  // v_from_k: a value row is the first vd entries of the key row (one vector per token serves as both).
   // vd: width of a value row (the keys' width is hd); NPL covers vd.  bias_r1 / bias_r2 [H]: with both
   // given, r1_h * ln(1 + r2_h * (i - j)) is taken off the scaled score of query i and key j (float32).
   // cross: every query head's weights are applied to the values of EVERY key/value head, one value head
@@ -318,8 +354,10 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
   extern __shared__ float smem[];
   float* qs = smem;                               // [ATT_ROWS][hd]
   float* Ks = qs + ATT_ROWS * hd;                 // [ATT_TK][hd + 1]
-  float* Vs = Ks + ATT_TK * (hd + 1);             // [ATT_TK][vd]
-  long long* rowoff = reinterpret_cast<long long*>(Vs + ATT_TK * vd + ((ATT_TK * (hd + 1) + ATT_TK * vd) & 1));  // [2][ATT_TK], 8-byte aligned
+  float* Vs = Ks + ATT_TK * (hd + 1);             // [ATT_TK][vd]; with v_from_k the key tile itself
+  const int vs_n = v_from_k ? 0 : ATT_TK * vd, vs_ld = v_from_k ? hd + 1 : vd;
+  long long* rowoff = reinterpret_cast<long long*>(Vs + vs_n + ((ATT_TK * (hd + 1) + vs_n) & 1));  // [2][ATT_TK], 8-byte aligned
+  if (v_from_k) Vs = Ks;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = H / Hkv;
@@ -371,11 +409,16 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
     const int first_hi = start + q0 + 1;
     k_begin = first_hi > window ? first_hi - window : 0;
   }
+  // the kept first tokens that lie below the window's reach: tiles [a_lo, a_hi), walked before the window's
+  int a_lo = 0, a_hi = (keep > 0 && k_begin > 0) ? min(keep, k_begin) : 0;
   if (num_splits > 1) {
     k_begin = max(k_begin, split * split_keys);
     k_end = min(k_end, (split + 1) * split_keys);
+    a_lo = split * split_keys;
+    a_hi = min(a_hi, (split + 1) * split_keys);
   }
   k_begin = (k_begin / ATT_TK) * ATT_TK;
+  a_hi = min(a_hi, k_begin);                      // a tile the window's walk reaches anyway is not walked twice
 
   float m[4], l[4], o[4][NPL];
 #pragma unroll
@@ -387,7 +430,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
   }
   const int split_lo = num_splits > 1 ? split * split_keys : 0;
 
-  for (int kb = k_begin; kb < k_end; kb += ATT_TK) {
+  for (int phase = 0; phase < 2; ++phase)
+  for (int kb = phase ? k_begin : a_lo; kb < (phase ? k_end : a_hi); kb += ATT_TK) {
     __syncthreads();  // previous tile fully consumed (and qs staged, first time)
     if (tid < ATT_TK) {
       const int kp = kb + tid;
@@ -405,7 +449,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
       const long long off = rowoff[j];
       Ks[j * (hd + 1) + d] = off >= 0 ? to_f32(k_cache[off * hd + d]) : 0.f;
     }
-    for (int idx = tid; idx < ATT_TK * vd; idx += ATT_WARPS * 32) {
+    for (int idx = tid; idx < vs_n; idx += ATT_WARPS * 32) {
       const int j = idx / vd, d = idx - j * vd;
       const long long off = rowoff[ATT_TK + j];
       Vs[j * vd + d] = off >= 0 ? to_f32(v_cache[off * vd + d]) : 0.f;
@@ -424,7 +468,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
     float p[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const bool ok = row_ok[i] && key_ok && kp >= row_lo[i] && kp < row_hi[i];
+      const bool ok = row_ok[i] && key_ok && (kp >= row_lo[i] || kp < keep) && kp < row_hi[i];
       float sc = -INFINITY;
       if (ok) {
         sc = s[i] * scale;
@@ -448,7 +492,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 #pragma unroll
       for (int c = 0; c < NPL; ++c) {
         const int d = lane + 32 * c;
-        vj[c] = d < vd ? Vs[j * vd + d] : 0.f;
+        vj[c] = d < vd ? Vs[j * vs_ld + d] : 0.f;
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -463,6 +507,14 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
   for (int i = 0; i < 4; ++i) {
     if (!row_ok[i]) continue;
     if (num_splits == 1 && !cross) {
+      if (sink) {                                 // one more term of the denominator
+        const float sk = sink[row_h[i]];
+        const float m_fin = fmaxf(m[i], sk);
+        const float alpha = m[i] == -INFINITY ? 0.f : expf(m[i] - m_fin);
+        l[i] = l[i] * alpha + expf(sk - m_fin);
+#pragma unroll
+        for (int c = 0; c < NPL; ++c) o[i][c] *= alpha;
+      }
       const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
       T* dst = out + (size_t)row_t[i] * H * vd + (size_t)row_h[i] * vd;
 #pragma unroll
@@ -489,21 +541,28 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 // (3) merge: out = sum_s e^{m_s - M} o_s / sum_s e^{m_s - M} l_s.  One warp per (token, head).
 // A lane holds the (m, l) of one chunk (32 chunks at a time), so that the loads of all chunks are
 // under way together; the sums run over the chunks in ascending order whatever the timing.
+// With `sink` [H] (rows ordered (token, head)): exp(sink_h) is one more term of the denominator.  Rows wider than
+// 256 values are merged 256 columns at a time.
 template <typename T>
-__global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                  T* __restrict__ out, int n_rows, int hd, int num_splits) {
+__global__ void attn_merge_kernel(const float* __restrict__ part_o_all, const float* __restrict__ part_ml,
+                                  T* __restrict__ out_all, int n_rows, int hd_all, int num_splits,
+                                  const float* __restrict__ sink, int H) {
   zk_let_next_start();
   zk_wait_prior();   // nothing of the kernels before is read, and nothing written, above this line
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= n_rows) return;
-  float M = -INFINITY;
+  float M = sink ? sink[row % H] : -INFINITY;
   for (int s0 = 0; s0 < num_splits; s0 += 32) {
     const int s = s0 + lane;
     const float ms = s < num_splits ? part_ml[((size_t)s * n_rows + row) * 2] : -INFINITY;
     M = fmaxf(M, warp_max(ms));
   }
-  float L = 0.f;
+  for (int c0 = 0; c0 < hd_all; c0 += 256) {
+  const int hd = min(256, hd_all - c0);
+  const float* part_o = part_o_all + c0;
+  T* out = out_all + c0;
+  float L = sink ? expf(sink[row % H] - M) : 0.f;
   float acc[8];   // head sizes up to 256: 8 values per lane
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
@@ -524,7 +583,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
       for (int u = 0; u < 8; ++u) {
         const int j = j0 + u;
         w[u] = j < n_here ? __shfl_sync(0xffffffffu, e, j & 31) : 0.f;
-        const float* po = part_o + ((size_t)(s0 + j) * n_rows + row) * hd;
+        const float* po = part_o + ((size_t)(s0 + j) * n_rows + row) * hd_all;
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[u][i] = (w[u] != 0.f && lane + 32 * i < hd) ? po[lane + 32 * i] : 0.f;
       }
@@ -537,7 +596,8 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
   const float inv = L > 0.f ? 1.0f / L : 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i)
-    if (lane + 32 * i < hd) out[(size_t)row * hd + lane + 32 * i] = from_f32<T>(acc[i] * inv);
+    if (lane + 32 * i < hd) out[(size_t)row * hd_all + lane + 32 * i] = from_f32<T>(acc[i] * inv);
+  }
 }
 
 // (3b) merge for weights that are mixed across the heads after the softmax: with w_g(i, j) head g's softmax
@@ -638,7 +698,7 @@ __global__ void __launch_bounds__(256)
 
 namespace {
 
-size_t attn_smem_bytes(int hd, int vd) {
+size_t attn_smem_bytes(int hd, int vd) {     // vd = 0: the values are read from the key tile
   return sizeof(float) * ((size_t)ATT_ROWS * hd + (size_t)ATT_TK * (hd + 1) + (size_t)ATT_TK * vd + 1) + sizeof(long long) * 2 * ATT_TK + 16;
 }
 
@@ -647,8 +707,9 @@ int launch_attn(const void* q, const void* k_cache, const void* v_cache, void* o
                 const int* tile_seq, const int* tile_q0, const int* cu_q, const int* seq_start, const int* seq_slot,
                 const int* page_table, int pt_stride, int n_tiles, int n_tokens, int H, int Hkv, int hd, int page_size,
                 int window, float scale, int bq, int gc, int num_splits, int split_keys, int vd, const float* r1,
-                const float* r2, int cross, cudaStream_t stream) {
-  const size_t smem = attn_smem_bytes(hd, vd);
+                const float* r2, int cross, int keep, const float* sink, int v_from_k, cudaStream_t stream) {
+  const size_t smem = attn_smem_bytes(hd, v_from_k ? 0 : vd);
+  if (smem > 227 * 1024) return ZK_EINVAL;
   auto kern = attn_fwd_kernel<T, NPL>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -660,7 +721,7 @@ int launch_attn(const void* q, const void* k_cache, const void* v_cache, void* o
   kern<<<grid, ATT_WARPS * 32, smem, stream>>>((const T*)q, (const T*)k_cache, (const T*)v_cache, (T*)out, part_o,
                                                part_ml, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table,
                                                pt_stride, n_tokens, H, Hkv, hd, page_size, window, scale, bq, gc,
-                                               num_splits, split_keys, vd, r1, r2, cross);
+                                               num_splits, split_keys, vd, r1, r2, cross, keep, sink, v_from_k);
   return ZK_LAUNCH_STATUS();
 }
 
@@ -669,15 +730,18 @@ int dispatch_attn(int hd, const void* q, const void* k_cache, const void* v_cach
                   float* part_ml, const int* tile_seq, const int* tile_q0, const int* cu_q, const int* seq_start,
                   const int* seq_slot, const int* page_table, int pt_stride, int n_tiles, int n_tokens, int H, int Hkv,
                   int page_size, int window, float scale, int bq, int gc, int num_splits, int split_keys, int vd,
-                  const float* r1, const float* r2, int cross, cudaStream_t stream) {
+                  const float* r1, const float* r2, int cross, int keep, const float* sink, int v_from_k,
+                  cudaStream_t stream) {
 #define ZK_ATT_CASE(N)                                                                                               \
   case N:                                                                                                            \
     return launch_attn<T, N>(q, k_cache, v_cache, out, part_o, part_ml, tile_seq, tile_q0, cu_q, seq_start, seq_slot, \
                              page_table, pt_stride, n_tiles, n_tokens, H, Hkv, hd, page_size, window, scale, bq, gc,  \
-                             num_splits, split_keys, vd, r1, r2, cross, stream);
-  switch ((vd + 31) / 32) {
+                             num_splits, split_keys, vd, r1, r2, cross, keep, sink, v_from_k, stream);
+  int npl = (vd + 31) / 32;                 // value columns per lane: every count up to 8, then 12, 16, 20
+  if (npl > 8) npl = npl <= 12 ? 12 : (npl <= 16 ? 16 : 20);
+  switch (npl) {
     ZK_ATT_CASE(1) ZK_ATT_CASE(2) ZK_ATT_CASE(3) ZK_ATT_CASE(4) ZK_ATT_CASE(5) ZK_ATT_CASE(6) ZK_ATT_CASE(7)
-    ZK_ATT_CASE(8)
+    ZK_ATT_CASE(8) ZK_ATT_CASE(12) ZK_ATT_CASE(16) ZK_ATT_CASE(20)
   }
 #undef ZK_ATT_CASE
   return ZK_EINVAL;
@@ -738,18 +802,34 @@ int zk_qk_prepare(const void* qkv, void* q_out, void* dense_out, void* k_cache, 
 int zk_qk_prepare_span(const void* qkv, int ld, void* q_out, void* k_cache, void* v_cache, const float* q_w,
                        const float* k_w, const int* tok_seq, const int* tok_pos, const int* seq_slot,
                        const int* page_table, int pt_stride, int n_tokens, int H, int Hkv, int hd, int vd, float eps,
-                       int page_size, int write_kv, int dtype, int* status, cudaStream_t stream) {
+                       int page_size, int write_kv, int dtype, int* status, const float* inv_freq, int n_rot,
+                       cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (hd <= 0 || vd <= 0 || H <= 0 || Hkv <= 0 || page_size <= 0) return ZK_EINVAL;
   if (ld < H * hd + (write_kv ? Hkv * (hd + vd) : 0)) return ZK_EINVAL;
-  if (dtype == ZK_F32)
-    return zk_launch_dependent(qk_prepare_span_kernel<float>, dim3(n_tokens, write_kv ? 2 : 1), dim3(SPAN_THREADS), 0, stream,
+  if (inv_freq && (n_rot <= 0 || (n_rot & 1) || n_rot > hd)) return ZK_EINVAL;
+  const size_t smem = inv_freq ? sizeof(float) * (size_t)(H > Hkv ? H : Hkv) * hd : 0;
+  if (smem > 160 * 1024) return ZK_EINVAL;
+  if (dtype == ZK_F32) {
+    auto kern = qk_prepare_span_kernel<float>;
+    if (smem > 40 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    return zk_launch_dependent(kern, dim3(n_tokens, write_kv ? 2 : 1), dim3(SPAN_THREADS), smem, stream,
         (const float*)qkv, ld, (float*)q_out, (float*)k_cache, (float*)v_cache, q_w, k_w, tok_seq, tok_pos, seq_slot,
-        page_table, pt_stride, H, Hkv, hd, vd, eps, page_size, status);
-  if (dtype == ZK_BF16)
-    return zk_launch_dependent(qk_prepare_span_kernel<bf16>, dim3(n_tokens, write_kv ? 2 : 1), dim3(SPAN_THREADS), 0, stream,
+        page_table, pt_stride, H, Hkv, hd, vd, eps, page_size, status, inv_freq, n_rot);
+  }
+  if (dtype == ZK_BF16) {
+    auto kern = qk_prepare_span_kernel<bf16>;
+    if (smem > 40 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    return zk_launch_dependent(kern, dim3(n_tokens, write_kv ? 2 : 1), dim3(SPAN_THREADS), smem, stream,
         (const bf16*)qkv, ld, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, q_w, k_w, tok_seq, tok_pos, seq_slot,
-        page_table, pt_stride, H, Hkv, hd, vd, eps, page_size, status);
+        page_table, pt_stride, H, Hkv, hd, vd, eps, page_size, status, inv_freq, n_rot);
+  }
   return ZK_EINVAL;
 }
 
@@ -759,8 +839,10 @@ int zk_attn_fwd(const void* q, const void* k_cache, const void* v_cache, void* o
                 const int* tile_seq, const int* tile_q0, const int* cu_q, const int* seq_start, const int* seq_slot,
                 const int* page_table, int pt_stride, int n_tiles, int n_tokens, int H, int Hkv, int hd, int page_size,
                 int window, float scale, int bq, int gc, int num_splits, int split_keys, int dtype, int vd,
-                const float* bias_r1, const float* bias_r2, int cross, cudaStream_t stream) {
+                const float* bias_r1, const float* bias_r2, int cross, int keep, const float* sink, int v_from_k,
+                cudaStream_t stream) {
   if (n_tiles <= 0 || n_tokens <= 0) return 0;
+  if (keep < 0 || (v_from_k && (vd > hd || cross))) return ZK_EINVAL;
   if (cross && (!part_o || !part_ml)) return ZK_EINVAL;
   if (hd <= 0 || hd > ATT_MAX_HD || H <= 0 || Hkv <= 0 || H % Hkv || page_size <= 0) return ZK_EINVAL;
   if (vd <= 0 || vd > ATT_MAX_HD || ((bias_r1 == nullptr) != (bias_r2 == nullptr))) return ZK_EINVAL;
@@ -769,11 +851,11 @@ int zk_attn_fwd(const void* q, const void* k_cache, const void* v_cache, void* o
   if (dtype == ZK_F32)
     return dispatch_attn<float>(hd, q, k_cache, v_cache, out, part_o, part_ml, tile_seq, tile_q0, cu_q, seq_start,
                                 seq_slot, page_table, pt_stride, n_tiles, n_tokens, H, Hkv, page_size, window, scale,
-                                bq, gc, num_splits, split_keys, vd, bias_r1, bias_r2, cross, stream);
+                                bq, gc, num_splits, split_keys, vd, bias_r1, bias_r2, cross, keep, sink, v_from_k, stream);
   if (dtype == ZK_BF16)
     return dispatch_attn<bf16>(hd, q, k_cache, v_cache, out, part_o, part_ml, tile_seq, tile_q0, cu_q, seq_start,
                                seq_slot, page_table, pt_stride, n_tiles, n_tokens, H, Hkv, page_size, window, scale, bq,
-                               gc, num_splits, split_keys, vd, bias_r1, bias_r2, cross, stream);
+                               gc, num_splits, split_keys, vd, bias_r1, bias_r2, cross, keep, sink, v_from_k, stream);
   return ZK_EINVAL;
 }
 
@@ -815,14 +897,15 @@ int zk_attn_merge_talk(const float* part_o, const float* part_ml, const float* t
 }
 
 int zk_attn_merge(const float* part_o, const float* part_ml, void* out, int n_rows, int hd, int num_splits, int dtype,
-                  cudaStream_t stream) {
+                  const float* sink, int H, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
+  if (sink && (H <= 0 || n_rows % H)) return ZK_EINVAL;
   const int warps = 4;
   const int blocks = (n_rows + warps - 1) / warps;
   if (dtype == ZK_F32)
-    return zk_launch_dependent(attn_merge_kernel<float>, dim3(blocks), dim3(warps * 32), 0, stream, part_o, part_ml, (float*)out, n_rows, hd, num_splits);
+    return zk_launch_dependent(attn_merge_kernel<float>, dim3(blocks), dim3(warps * 32), 0, stream, part_o, part_ml, (float*)out, n_rows, hd, num_splits, sink, H);
   else if (dtype == ZK_BF16)
-    return zk_launch_dependent(attn_merge_kernel<bf16>, dim3(blocks), dim3(warps * 32), 0, stream, part_o, part_ml, (bf16*)out, n_rows, hd, num_splits);
+    return zk_launch_dependent(attn_merge_kernel<bf16>, dim3(blocks), dim3(warps * 32), 0, stream, part_o, part_ml, (bf16*)out, n_rows, hd, num_splits, sink, H);
   else
     return ZK_EINVAL;
   return ZK_LAUNCH_STATUS();

@@ -112,6 +112,37 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ h, int
   }
 }
 
+// The gated unit of a feed-forward whose gate is capped and whose linear branch is clamped and shifted:
+//   g <- min(g, limit), u <- clamp(u, -limit, limit), h = g * sigmoid(alpha * g) * (u + 1)   (float32 arithmetic).
+// Rows of gu as in silu_mul_kernel.
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ h, int n, int F, int il, float limit, float alpha) {
+  zk_let_next_start();
+  zk_wait_prior();
+  const size_t total = (size_t)n * F;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / F, f = i - t * F;
+    const size_t gi = il ? (f / il) * 2 * il + f % il : f;
+    const size_t ui = il ? gi + il : F + f;
+    const float g = fminf(to_f32(gu[t * 2 * F + gi]), limit);
+    const float u = fminf(fmaxf(to_f32(gu[t * 2 * F + ui]), -limit), limit);
+    h[i] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+  }
+}
+
+// A gate per (token, head): rows[t, h, :] *= sigmoid(gate[t * ld_gate + h]), gate float32, in place.
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ rows, const float* __restrict__ gate, int ld_gate, int n, int H, int width) {
+  zk_let_next_start();
+  zk_wait_prior();
+  const size_t total = (size_t)n * H * width;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t th = i / width, t = th / H, hh = th - t * H;
+    const float g = gate[t * ld_gate + hh];
+    rows[i] = from_f32<T>(to_f32(rows[i]) / (1.0f + expf(-g)));
+  }
+}
+
 // out[i] = mean + std * n_i with n_i standard normal, a function of (seed, i) only: two hashed
 // uniforms through Box-Muller.  Fills large random models on the device in milliseconds.
 __device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
@@ -685,6 +716,28 @@ int zk_norm_shift(const float* x, const float* w, const float* mu, float* state,
   if (rc != 0 || single_token) return rc;
   return zk_launch_dependent(norm_shift_state_kernel, dim3(n_seqs), dim3(threads), 0, stream, x, w, state, state_stride,
                              cu_q, seq_slot, dim, eps, vec4 ? 1 : 0);
+}
+
+int zk_clamped_glu(const void* gu, void* h, int n, int F, int il, float limit, float alpha, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (F <= 0 || il < 0 || (il > 0 && F % il)) return ZK_EINVAL;
+  const int threads = 256, blocks = grid_for_total((size_t)n * F, threads);
+  if (dtype == ZK_F32)
+    return zk_launch_dependent(clamped_glu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gu, (float*)h, n, F, il, limit, alpha);
+  if (dtype == ZK_BF16)
+    return zk_launch_dependent(clamped_glu_kernel<bf16>, dim3(blocks), dim3(threads), 0, stream, (const bf16*)gu, (bf16*)h, n, F, il, limit, alpha);
+  return ZK_EINVAL;
+}
+
+int zk_head_gate(void* rows, const float* gate, int ld_gate, int n, int H, int width, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (H <= 0 || width <= 0 || ld_gate < H) return ZK_EINVAL;
+  const int threads = 256, blocks = grid_for_total((size_t)n * H * width, threads);
+  if (dtype == ZK_F32)
+    return zk_launch_dependent(head_gate_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)rows, gate, ld_gate, n, H, width);
+  if (dtype == ZK_BF16)
+    return zk_launch_dependent(head_gate_kernel<bf16>, dim3(blocks), dim3(threads), 0, stream, (bf16*)rows, gate, ld_gate, n, H, width);
+  return ZK_EINVAL;
 }
 
 int zk_gate_add(const float* x, const float* g, const float* s, float* m, int n, int dim, int out_dim, cudaStream_t stream) {

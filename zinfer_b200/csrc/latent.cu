@@ -1,0 +1,164 @@
+// Attention whose keys and values are expanded from one latent vector per token.
+//
+// Per token the cache holds ONE row [c (r) | k_rot (p)]: c the RMS-normalised latent, k_rot a rotated key part
+// that all heads share.  With W_uk [H*d, r] and W_uv [H*e, r] the expansions k_h = W_uk,h c and v_h = W_uv,h c are
+// never made for cached tokens: a head's query is carried into the latent's space, q'_h = [W_uk,h^T q_h | rot(q_rot,h)],
+// so that q'_h . row = q_h . k_h + rot(q_rot,h) . k_rot, the softmax weights are applied to c itself, and W_uv,h
+// expands the weighted sum afterwards.  Attention is then multi-query attention over rows of r + p values whose
+// first r values are also the "value".
+//
+// (1) latent_prepare_kernel: norm of the latent, rotation of the shared key part, cache write; rotation of the
+//     queries' rotated parts into their place behind the r latent-space columns.
+// (2) head_gemm_kernel: out[t, h, :] = a[t, h, :] W[h]^T for few tokens, weights streamed once (the two per-head
+//     steps around attention in single-token steps), with an optional sigmoid gate per (token, head).
+#include "common.cuh"
+#include <math.h>
+
+#define LAT_THREADS 256
+
+// Block (t, 0): rotated query parts.  q [n, H * (d + p)] as the projection left it (head by head [d | p]); the
+// rotated p entries of head h go to q_full[t, h, r .. r + p) (rows of H * (r + p); the first r columns of every
+// head are written by the contraction that follows).  Block (t, 1): the token's cache row from dkv (float32, rows
+// `ld_dkv` apart): [rms(dkv[:r]) * w | rot(dkv[r : r + p])].  Pairs (i, i + p/2), angle = float(pos) * inv_freq[i].
+template <typename T>
+__global__ void __launch_bounds__(LAT_THREADS)
+    latent_prepare_kernel(const T* __restrict__ q, T* __restrict__ q_full, const float* __restrict__ dkv, int ld_dkv,
+                          const float* __restrict__ c_w, const float* __restrict__ inv_freq, T* __restrict__ cache,
+                          const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                          const int* __restrict__ seq_slot, const int* __restrict__ page_table, int pt_stride, int H,
+                          int d, int p, int r, float eps, int page_size, int write_kv, int* status) {
+  __shared__ float scratch[32];
+  zk_let_next_start();
+  zk_wait_prior();
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const int pos = tok_pos[t];
+  const int half = p >> 1;
+  if (blockIdx.y == 0) {
+    for (int idx = tid; idx < H * half; idx += LAT_THREADS) {
+      const int h = idx / half, i = idx - h * half;
+      const T* src = q + ((size_t)t * H + h) * (d + p) + d;
+      const float ang = (float)pos * inv_freq[i];
+      const float c = cosf(ang), sn = sinf(ang);
+      const float u = to_f32(src[i]), v = to_f32(src[i + half]);
+      T* dst = q_full + ((size_t)t * H + h) * (r + p) + r;
+      dst[i] = from_f32<T>(u * c - v * sn);
+      dst[i + half] = from_f32<T>(u * sn + v * c);
+    }
+    return;
+  }
+  if (!write_kv) return;
+  const int page = page_table[(size_t)seq_slot[tok_seq[t]] * pt_stride + pos / page_size];
+  if (page < 0) {
+    if (tid == 0) atomicExch(status, 2);
+    return;
+  }
+  T* row = cache + ((size_t)page * page_size + pos % page_size) * (r + p);
+  const float* src = dkv + (size_t)t * ld_dkv;
+  float ss = 0.f;
+  for (int i = tid; i < r; i += LAT_THREADS) ss = fmaf(src[i], src[i], ss);
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)r + eps);
+  for (int i = tid; i < r; i += LAT_THREADS) row[i] = from_f32<T>((src[i] * scale) * c_w[i]);
+  for (int i = tid; i < half; i += LAT_THREADS) {
+    const float ang = (float)pos * inv_freq[i];
+    const float c = cosf(ang), sn = sinf(ang);
+    const float u = src[r + i], v = src[r + i + half];
+    row[r + i] = from_f32<T>(u * c - v * sn);
+    row[r + i + half] = from_f32<T>(u * sn + v * c);
+  }
+}
+
+// out[t, h, n] = (sum_k a[t, h, k] * w[h, n, k]) * (gate ? sigmoid(gate[t * ld_gate + h]) : 1).
+// a rows `lda` apart with head h at column h * a_head; out rows `ldo` apart with head h at column h * o_head;
+// w [H, N, K] contiguous.  Block = (head, slice of N, group of LAT_ROWS tokens): the tokens' inputs wait in shared
+// memory as float32, a warp owns an output column at a time and its lanes walk K, so every weight is read once per
+// group of tokens and a sum's order depends on nothing but K.
+#define LAT_ROWS 8
+template <typename T>
+__global__ void __launch_bounds__(LAT_THREADS)
+    head_gemm_kernel(const T* __restrict__ a, int lda, int a_head, const T* __restrict__ w, T* __restrict__ out, int ldo,
+                     int o_head, const float* __restrict__ gate, int ld_gate, int n, int N, int K, int cols_per_block) {
+  extern __shared__ float as[];     // [LAT_ROWS][K]
+  zk_let_next_start();
+  zk_wait_prior();
+  const int h = blockIdx.x, t0 = blockIdx.z * LAT_ROWS;
+  const int rows = min(LAT_ROWS, n - t0);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = LAT_THREADS / 32;
+  for (int idx = threadIdx.x; idx < LAT_ROWS * K; idx += LAT_THREADS) {
+    const int rr = idx / K, k = idx - rr * K;
+    as[idx] = rr < rows ? to_f32(a[(size_t)(t0 + rr) * lda + (size_t)h * a_head + k]) : 0.f;
+  }
+  __syncthreads();
+  const int c0 = blockIdx.y * cols_per_block, c1 = min(N, c0 + cols_per_block);
+  for (int col = c0 + warp; col < c1; col += nw) {
+    const T* wr = w + ((size_t)h * N + col) * K;
+    float acc[LAT_ROWS];
+#pragma unroll
+    for (int rr = 0; rr < LAT_ROWS; ++rr) acc[rr] = 0.f;
+    for (int k = lane; k < K; k += 32) {
+      const float wv = to_f32(wr[k]);
+#pragma unroll
+      for (int rr = 0; rr < LAT_ROWS; ++rr) acc[rr] = fmaf(as[rr * K + k], wv, acc[rr]);
+    }
+#pragma unroll
+    for (int rr = 0; rr < LAT_ROWS; ++rr) acc[rr] = warp_sum(acc[rr]);
+    if (lane < rows) {
+      float v = 0.f;
+#pragma unroll
+      for (int rr = 0; rr < LAT_ROWS; ++rr)
+        if (lane == rr) v = acc[rr];
+      if (gate) v = v / (1.0f + expf(-gate[(size_t)(t0 + lane) * ld_gate + h]));
+      out[(size_t)(t0 + lane) * ldo + (size_t)h * o_head + col] = from_f32<T>(v);
+    }
+  }
+}
+
+extern "C" {
+
+int zk_latent_prepare(const void* q, void* q_full, const float* dkv, int ld_dkv, const float* c_w, const float* inv_freq,
+                      void* cache, const int* tok_seq, const int* tok_pos, const int* seq_slot, const int* page_table,
+                      int pt_stride, int n_tokens, int H, int d, int p, int r, float eps, int page_size, int write_kv,
+                      int dtype, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (H <= 0 || d <= 0 || p <= 0 || (p & 1) || r <= 0 || page_size <= 0 || ld_dkv < r + p || !inv_freq || !c_w) return ZK_EINVAL;
+  const dim3 grid(n_tokens, 2);
+  if (dtype == ZK_F32)
+    return zk_launch_dependent(latent_prepare_kernel<float>, grid, dim3(LAT_THREADS), 0, stream, (const float*)q, (float*)q_full,
+                               dkv, ld_dkv, c_w, inv_freq, (float*)cache, tok_seq, tok_pos, seq_slot, page_table, pt_stride,
+                               H, d, p, r, eps, page_size, write_kv, status);
+  if (dtype == ZK_BF16)
+    return zk_launch_dependent(latent_prepare_kernel<bf16>, grid, dim3(LAT_THREADS), 0, stream, (const bf16*)q, (bf16*)q_full,
+                               dkv, ld_dkv, c_w, inv_freq, (bf16*)cache, tok_seq, tok_pos, seq_slot, page_table, pt_stride,
+                               H, d, p, r, eps, page_size, write_kv, status);
+  return ZK_EINVAL;
+}
+
+int zk_head_gemm(const void* a, int lda, int a_head, const void* w, void* out, int ldo, int o_head, const float* gate,
+                 int ld_gate, int n, int H, int N, int K, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (H <= 0 || N <= 0 || K <= 0 || lda < 0 || ldo < 0) return ZK_EINVAL;
+  const size_t smem = sizeof(float) * LAT_ROWS * (size_t)K;
+  if (smem > 200 * 1024) return ZK_EINVAL;
+  const int groups = (n + LAT_ROWS - 1) / LAT_ROWS;
+  int cols = N;                                    // enough blocks for the GPU when the tokens are few
+  while (cols > 8 && (long long)H * groups * ((N + cols - 1) / cols) < 2 * 148) cols = (cols + 1) / 2;
+  cols = (cols + 7) / 8 * 8;
+  const dim3 grid(H, (N + cols - 1) / cols, groups);
+  if (grid.y > 65535 || grid.z > 65535) return ZK_EINVAL;
+#define ZK_HG(T)                                                                                                     \
+  do {                                                                                                               \
+    auto kern = head_gemm_kernel<T>;                                                                                 \
+    if (smem > 48 * 1024) {                                                                                          \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+      if (e != cudaSuccess) return (int)e;                                                                           \
+    }                                                                                                                \
+    return zk_launch_dependent(kern, grid, dim3(LAT_THREADS), smem, stream, (const T*)a, lda, a_head, (const T*)w,   \
+                               (T*)out, ldo, o_head, gate, ld_gate, n, N, K, cols);                                  \
+  } while (0)
+  if (dtype == ZK_F32) ZK_HG(float);
+  if (dtype == ZK_BF16) ZK_HG(bf16);
+#undef ZK_HG
+  return ZK_EINVAL;
+}
+
+}  // extern "C"

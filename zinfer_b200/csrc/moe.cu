@@ -74,8 +74,18 @@ __device__ __forceinline__ void rows_dot(const T* const (&w)[R], const float* __
 
 #define MOE_UNITS 4      // hidden units (gate and up row each) or outputs a warp works on at once
 
+// With `tokens` null the experts are not looked up through a table: `table` is then [n, top], the experts a
+// router chose for each token.
 __device__ __forceinline__ int moe_expert(const int* __restrict__ tokens, const int* __restrict__ table, int t, int k,
                                           int top, int vocab, int n_experts, int* status) {
+  if (!tokens) {
+    int e = table[(size_t)t * top + k];
+    if (e < 0 || e >= n_experts) {
+      if (threadIdx.x == 0) atomicExch(status, 4);
+      e = 0;
+    }
+    return e;
+  }
   int tok = tokens[t];
   if (tok < 0 || tok >= vocab) tok = 0;        // the embedding kernel has flagged it
   int e = table[(size_t)tok * top + k];
@@ -130,7 +140,8 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
     moe_down_kernel(const T* __restrict__ h, const int* __restrict__ tokens, const int* __restrict__ table,
                     const T* __restrict__ w_down, float* __restrict__ y, int D, int F, int top, int vocab,
-                    int n_experts, int outs_per_block, int accumulate, int* status) {
+                    int n_experts, int outs_per_block, int accumulate, int* status, const float* __restrict__ route_w) {
+  // route_w [n, top]: the weight of each of the token's experts (null: 1/top each)
   extern __shared__ float hs[];     // [top][F]
   zk_let_next_start();
   zk_wait_prior();
@@ -152,7 +163,9 @@ __global__ void __launch_bounds__(MOE_WARPS * 32)
       float dot[MOE_UNITS];
       rows_dot<T, VEC, MOE_UNITS>(rows, hs + (size_t)k * F, F, lane, dot);
 #pragma unroll
-      for (int u = 0; u < MOE_UNITS; ++u) acc[u] += weight * dot[u];
+      const float wk = route_w ? route_w[(size_t)t * top + k] : weight;
+#pragma unroll
+      for (int u = 0; u < MOE_UNITS; ++u) acc[u] += wk * dot[u];
     }
     if (lane < MOE_UNITS && db + lane < d1) {
       float v = 0.f;
@@ -183,16 +196,84 @@ __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict
 }
 
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_row, float* __restrict__ out,
-                                   int D, int top, int accumulate) {
+                                   int D, int top, int accumulate, const float* __restrict__ route_w) {
   zk_let_next_start();
   zk_wait_prior();
   const int t = blockIdx.x;
   const float weight = 1.0f / (float)top;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float acc = 0.f;
-    for (int k = 0; k < top; ++k) acc += weight * y[(size_t)pair_row[t * top + k] * D + d];
+    for (int k = 0; k < top; ++k)
+      acc += (route_w ? route_w[(size_t)t * top + k] : weight) * y[(size_t)pair_row[t * top + k] * D + d];
     out[(size_t)t * D + d] = accumulate ? out[(size_t)t * D + d] + acc : acc;
   }
+}
+
+// Router of a mixture of experts, one block per token.  The logits are float32 dot products (a warp per expert,
+// lanes striding the row, sums in lane order then the warp's tree), the softmax runs over all E experts, and warp 0
+// then picks the `top` largest scores one after the other (of equal scores the lower index first).
+#define MOE_ROUTER_MAX_EXPERTS 4096
+template <typename T>
+__global__ void __launch_bounds__(MOE_WARPS * 32)
+    moe_router_kernel(const T* __restrict__ x, const float* __restrict__ w, int* __restrict__ ids, float* __restrict__ wts,
+                      int D, int E, int top) {
+  extern __shared__ float rs[];     // [D] the token's row, [E] logits then scores
+  float* xs = rs;
+  float* z = rs + D;
+  zk_let_next_start();
+  zk_wait_prior();
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) xs[d] = to_f32(x[(size_t)t * D + d]);
+  __syncthreads();
+  for (int e = warp; e < E; e += MOE_WARPS) {
+    const float* wr = w + (size_t)e * D;
+    float acc = 0.f;
+    for (int d = lane; d < D; d += 32) acc = fmaf(wr[d], xs[d], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) z[e] = acc;
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float m = -INFINITY;
+  for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
+  m = warp_max(m);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float v = expf(z[e] - m);
+    z[e] = v;
+    sum += v;
+  }
+  sum = warp_sum(sum);
+  __syncwarp();
+  float chosen_sum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -1.f;
+    int arg = E;
+    for (int e = lane; e < E; e += 32)
+      if (z[e] > best) {          // ascending e within a lane: the lower index wins a tie
+        best = z[e];
+        arg = e;
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) {
+        best = ob;
+        arg = oa;
+      }
+    }
+    if (lane == 0) {
+      ids[(size_t)t * top + k] = arg;
+      wts[(size_t)t * top + k] = best / sum;
+      z[arg] = -2.f;              // taken
+    }
+    chosen_sum += best / sum;
+    __syncwarp();
+  }
+  const float inv = 1.0f / (chosen_sum + 1e-20f);
+  __syncwarp();
+  for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] *= inv;
 }
 
 namespace {
@@ -200,7 +281,7 @@ namespace {
 template <typename T>
 int launch_moe(const void* x, const int* tokens, const int* table, const void* w_gu, int il,
                const void* w_down, void* h, float* y, int n, int D, int F, int top, int vocab, int n_experts,
-               int accumulate, int* status, cudaStream_t stream) {
+               int accumulate, int* status, const float* route_w, cudaStream_t stream) {
   const int per = 16 / (int)sizeof(T);   // elements per 16 bytes
   auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   const bool vec_gu = D % 8 == 0 && D % per == 0 && aligned(w_gu);
@@ -235,7 +316,7 @@ int launch_moe(const void* x, const int* tokens, const int* table, const void* w
       if (e != cudaSuccess) return (int)e;                                                                            \
     }                                                                                                                 \
     rc = zk_launch_dependent(kern, grid_dn, dim3(MOE_WARPS * 32), smem_dn, stream, (const T*)h, tokens, table,        \
-                             (const T*)w_down, y, D, F, top, vocab, n_experts, outs, accumulate, status);             \
+                             (const T*)w_down, y, D, F, top, vocab, n_experts, outs, accumulate, status, route_w);    \
   } while (0)
   if (vec_gu) ZK_MOE_GU(true); else ZK_MOE_GU(false);
   if (rc != 0) return rc;
@@ -257,9 +338,47 @@ int zk_moe_table(const void* x, const int* tokens, const int* table, const void*
   if (n <= 0) return 0;
   if (D <= 0 || F <= 0 || top <= 0 || vocab <= 0 || n_experts <= 0 || il < 0 || (il > 0 && F % il)) return ZK_EINVAL;
   if (dtype == ZK_F32)
-    return launch_moe<float>(x, tokens, table, w_gu, il, w_down, h, y, n, D, F, top, vocab, n_experts, accumulate, status, stream);
+    return launch_moe<float>(x, tokens, table, w_gu, il, w_down, h, y, n, D, F, top, vocab, n_experts, accumulate, status, nullptr, stream);
   if (dtype == ZK_BF16)
-    return launch_moe<bf16>(x, tokens, table, w_gu, il, w_down, h, y, n, D, F, top, vocab, n_experts, accumulate, status, stream);
+    return launch_moe<bf16>(x, tokens, table, w_gu, il, w_down, h, y, n, D, F, top, vocab, n_experts, accumulate, status, nullptr, stream);
+  return ZK_EINVAL;
+}
+
+// The same with the experts a router chose: route_ids [n, top] int32 and route_w [n, top] float32 (the weight of
+// each), y_t = sum_k route_w[t, k] * Expert[route_ids[t, k]](x_t), added in the order of k.
+int zk_moe_routed(const void* x, const int* route_ids, const float* route_w, const void* w_gu, int il, const void* w_down,
+                  void* h, float* y, int n, int D, int F, int top, int n_experts, int accumulate, int dtype, int* status,
+                  cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (D <= 0 || F <= 0 || top <= 0 || n_experts <= 0 || il < 0 || (il > 0 && F % il) || !route_ids || !route_w) return ZK_EINVAL;
+  if (dtype == ZK_F32)
+    return launch_moe<float>(x, nullptr, route_ids, w_gu, il, w_down, h, y, n, D, F, top, 1, n_experts, accumulate, status, route_w, stream);
+  if (dtype == ZK_BF16)
+    return launch_moe<bf16>(x, nullptr, route_ids, w_gu, il, w_down, h, y, n, D, F, top, 1, n_experts, accumulate, status, route_w, stream);
+  return ZK_EINVAL;
+}
+
+// Router: z = W x_t in float32 (W [E, D] float32, x in the run dtype), s = softmax(z) over all experts, the `top`
+// largest s (ties: the lower index) are chosen and weighed s / (sum of the chosen + 1e-20).
+int zk_moe_router(const void* x, const float* w_router, int* route_ids, float* route_w, int n, int D, int E, int top,
+                  int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (D <= 0 || E <= 0 || top <= 0 || top > E || E > MOE_ROUTER_MAX_EXPERTS) return ZK_EINVAL;
+  const size_t smem = sizeof(float) * ((size_t)D + E);
+  if (smem > 200 * 1024) return ZK_EINVAL;
+#define ZK_ROUTER(T)                                                                                                 \
+  do {                                                                                                               \
+    auto kern = moe_router_kernel<T>;                                                                                \
+    if (smem > 48 * 1024) {                                                                                          \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+      if (e != cudaSuccess) return (int)e;                                                                           \
+    }                                                                                                                \
+    return zk_launch_dependent(kern, dim3(n), dim3(MOE_WARPS * 32), smem, stream, (const T*)x, w_router, route_ids,  \
+                               route_w, D, E, top);                                                                  \
+  } while (0)
+  if (dtype == ZK_F32) ZK_ROUTER(float);
+  if (dtype == ZK_BF16) ZK_ROUTER(bf16);
+#undef ZK_ROUTER
   return ZK_EINVAL;
 }
 
@@ -277,10 +396,10 @@ int zk_moe_gather(const void* x, const int* row_token, void* xg, int n_rows, int
 
 // out[t, :] (=|+=) (1/top) * sum_k y[pair_row[t * top + k], :], float32, added in the order of k.
 int zk_moe_combine(const float* y, const int* pair_row, float* out, int n, int D, int top, int accumulate,
-                   cudaStream_t stream) {
+                   const float* route_w, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (D <= 0 || top <= 0) return ZK_EINVAL;
-  return zk_launch_dependent(moe_combine_kernel, dim3(n), dim3(128), 0, stream, y, pair_row, out, D, top, accumulate);
+  return zk_launch_dependent(moe_combine_kernel, dim3(n), dim3(128), 0, stream, y, pair_row, out, D, top, accumulate, route_w);
 }
 
 }  // extern "C"

@@ -37,6 +37,12 @@ _SIGNATURES = {
         "zk_scale_add": "ppplip",
         "zk_rows_add": "ppplip",
         "zk_norm_shift": "pppplppppiiifiip",
+        "zk_clamped_glu": "ppiiiffip",
+        "zk_head_gate": "ppiiiiip",
+    },
+    "latent": {
+        "zk_latent_prepare": "pppi" + "ppppppp" + "iiiiii" + "f" + "iii" + "pp",
+        "zk_head_gemm": "piippiipiiiiiip",
     },
     "hgrn2": {
         "zk_hgrn2_scan": "pippplpppiiiiip",
@@ -50,7 +56,9 @@ _SIGNATURES = {
     "moe": {
         "zk_moe_table": "ppppippp" + "iiiiiiiipp",
         "zk_moe_gather": "pppiiip",
-        "zk_moe_combine": "pppiiiip",
+        "zk_moe_combine": "pppiiii" + "p" + "p",
+        "zk_moe_routed": "ppppippp" + "iiiiiii" + "pp",
+        "zk_moe_router": "pppp" + "iiiii" + "p",
     },
     "gemm_simt": {
         "zk_gemm_simt": "ppppiiiiiiiiip",
@@ -105,10 +113,10 @@ _SIGNATURES = {
     },
     "attention": {
         "zk_qk_prepare": "pppppppppppp" + "iiiiiiifiiip" + "ii" + "p",
-        "zk_qk_prepare_span": "pipppppppppiiiiiifiiipp",
-        "zk_attn_fwd": "pppppp" + "pppppp" + "iiiiiiiifiiiii" + "ippi" + "p",
+        "zk_qk_prepare_span": "pipppppppppiiiiiifiiip" + "pi" + "p",
+        "zk_attn_fwd": "pppppp" + "pppppp" + "iiiiiiiifiiiii" + "ippi" + "ipi" + "p",
         "zk_attn_merge_talk": "ppppiiiiiip",
-        "zk_attn_merge": "pppiiiip",
+        "zk_attn_merge": "pppiiii" + "pi" + "p",
         "zk_attn_rows_per_block": "",
         "zk_attn_max_head_dim": "",
     },
@@ -468,6 +476,32 @@ def silu_mul(gu: torch.Tensor, interleave: int = 0) -> torch.Tensor:
     _check(_fn("elementwise", "zk_silu_mul")(_ptr(gu), _ptr(h), n, two_f // 2, interleave, dtype_code(gu.dtype),
                                              _stream()), "silu_mul")
     return h
+
+
+def clamped_glu(gu: torch.Tensor, limit: float, alpha: float, interleave: int = 0) -> torch.Tensor:
+    """h = g' * sigmoid(alpha * g') * (u' + 1) with g' = min(gate, limit), u' = clamp(up, -limit, limit), in float32
+    arithmetic.  Rows of gu as in `silu_mul`."""
+    _need(gu, "gu", (torch.float32, torch.bfloat16), (None, None))
+    n, two_f = gu.shape
+    if two_f % 2 or (interleave and (two_f // 2) % interleave):
+        raise KernelError(f"clamped_glu: width {two_f} does not split into gate and up (groups of {interleave})")
+    h = torch.empty((n, two_f // 2), dtype=gu.dtype, device=gu.device)
+    _check(_fn("elementwise", "zk_clamped_glu")(_ptr(gu), _ptr(h), n, two_f // 2, interleave, float(limit), float(alpha),
+                                                dtype_code(gu.dtype), _stream()), "clamped_glu")
+    return h
+
+
+def head_gate(rows: torch.Tensor, gate: torch.Tensor, n_heads: int) -> torch.Tensor:
+    """rows[t, h, :] *= sigmoid(gate[t, h]) in place.  rows [n, H * width] contiguous; gate float32 [n, >= H] (a view
+    of wider rows is fine: its row stride is used)."""
+    _need(rows, "rows", (torch.float32, torch.bfloat16), (None, None))
+    n, w = rows.shape
+    _need(gate, "gate", torch.float32, (n, None), contiguous=False)
+    if w % n_heads or gate.shape[1] < n_heads or gate.stride(1) != 1:
+        raise KernelError(f"head_gate: rows {tuple(rows.shape)} / gate {tuple(gate.shape)} do not fit {n_heads} heads")
+    _check(_fn("elementwise", "zk_head_gate")(_ptr(rows), _ptr(gate), gate.stride(0), n, n_heads, w // n_heads,
+                                              dtype_code(rows.dtype), _stream()), "head_gate")
+    return rows
 
 
 def fill_normal(out: torch.Tensor, seed: int, mean: float = 0.0, std: float = 1.0) -> torch.Tensor:
@@ -889,13 +923,109 @@ def moe_gather(x: torch.Tensor, row_token: torch.Tensor) -> torch.Tensor:
     return xg
 
 
-def moe_combine(y: torch.Tensor, pair_row: torch.Tensor, top: int, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
-    """out[t] (+)= (1/top) sum_k y[pair_row[t * top + k]], float32, added in the order of k."""
+def moe_combine(y: torch.Tensor, pair_row: torch.Tensor, top: int, out: torch.Tensor, accumulate: bool = False,
+                weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] (+)= sum_k weights[t, k] * y[pair_row[t * top + k]] (weights float32 [n, top]; without them 1/top
+    each), float32, added in the order of k."""
     _need(y, "y", torch.float32, (None, None))
     _need(out, "out", torch.float32, (None, y.shape[1]))
     _need(pair_row, "pair_row", torch.int32, (out.shape[0] * top,))
+    if weights is not None:
+        _need(weights, "weights", torch.float32, (out.shape[0], top))
     _check(_fn("moe", "zk_moe_combine")(_ptr(y), _ptr(pair_row), _ptr(out), out.shape[0], y.shape[1], top,
-                                        1 if accumulate else 0, _stream()), "moe_combine")
+                                        1 if accumulate else 0, _ptr(weights), _stream()), "moe_combine")
+    return out
+
+
+def moe_router(x: torch.Tensor, w_router: torch.Tensor, top: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """(experts int32 [n, top], weights float32 [n, top]) of every row of x [n, D] (run dtype): logits W x in
+    float32 (w_router float32 [E, D]), softmax over all E experts, the `top` largest scores (of equal ones the
+    lower index), each divided by the sum of the chosen (+ 1e-20)."""
+    _need(x, "x", (torch.float32, torch.bfloat16), (None, None))
+    n, D = x.shape
+    _need(w_router, "w_router", torch.float32, (None, D))
+    E = w_router.shape[0]
+    if not 0 < top <= E:
+        raise KernelError(f"moe_router: {top} experts per token out of {E}")
+    ids = torch.empty((n, top), dtype=torch.int32, device=x.device)
+    wts = torch.empty((n, top), dtype=torch.float32, device=x.device)
+    _check(_fn("moe", "zk_moe_router")(_ptr(x), _ptr(w_router), _ptr(ids), _ptr(wts), n, D, E, top, dtype_code(x.dtype),
+                                       _stream()), "moe_router")
+    return ids, wts
+
+
+def moe_routed(x: torch.Tensor, route_ids: torch.Tensor, route_w: torch.Tensor, w_gate_up: torch.Tensor, interleave: int,
+               w_down: torch.Tensor, status: torch.Tensor, out: Optional[torch.Tensor] = None,
+               accumulate: bool = False) -> torch.Tensor:
+    """y[t] = sum_k route_w[t, k] * W_down[e] (silu(W_gate[e] x_t) * (W_up[e] x_t)), e = route_ids[t, k], added in
+    the order of k.  Tensors as in `moe_table`."""
+    _need(x, "x", (torch.float32, torch.bfloat16), (None, None))
+    n, D = x.shape
+    _need(route_ids, "route_ids", torch.int32, (n, None))
+    top = route_ids.shape[1]
+    _need(route_w, "route_w", torch.float32, (n, top))
+    _need(w_gate_up, "w_gate_up", x.dtype, (None, None, D))
+    E, F = w_gate_up.shape[0], w_gate_up.shape[1] // 2
+    _need(w_down, "w_down", x.dtype, (E, D, F))
+    if out is None:
+        if accumulate:
+            raise KernelError("moe_routed: accumulate needs an output tensor")
+        out = torch.empty((n, D), dtype=torch.float32, device=x.device)
+    _need(out, "out", torch.float32, (n, D))
+    h = torch.empty((n, top, F), dtype=x.dtype, device=x.device)
+    _check(_fn("moe", "zk_moe_routed")(_ptr(x), _ptr(route_ids), _ptr(route_w), _ptr(w_gate_up), int(interleave), _ptr(w_down),
+                                       _ptr(h), _ptr(out), n, D, F, top, E, 1 if accumulate else 0, dtype_code(x.dtype),
+                                       _ptr(status), _stream()), "moe_routed")
+    return out
+
+
+# ------------------------------------------------------------------------------- one latent vector per token
+
+def latent_prepare(q: torch.Tensor, q_full: torch.Tensor, dkv: torch.Tensor, c_weight: torch.Tensor, inv_freq: torch.Tensor,
+                   cache: torch.Tensor, tok_seq, tok_pos, seq_slot, page_table, n_heads: int, dim: int, rot_dim: int,
+                   rank: int, eps: float, status, write_kv: bool = True) -> None:
+    """For attention over one latent row per token.  q [n, H * (dim + rot_dim)] (run dtype) as projected; the rotated
+    part of every head goes, rotated by the token's position, to q_full[:, h, rank : rank + rot_dim] (q_full
+    [n, H * (rank + rot_dim)]).  dkv float32 [n, >= rank + rot_dim] (a view of wider rows is fine): the token's
+    cache row becomes [rms(dkv[:rank]) * c_weight | rotated dkv[rank : rank + rot_dim]]; cache is one layer's
+    [pages, 1, page_size, rank + rot_dim]."""
+    _need(q, "q", (torch.float32, torch.bfloat16), (None, n_heads * (dim + rot_dim)))
+    n = q.shape[0]
+    _need(q_full, "q_full", q.dtype, (n, n_heads * (rank + rot_dim)))
+    _need(dkv, "dkv", torch.float32, (n, None), contiguous=False)
+    if dkv.shape[1] < rank + rot_dim or dkv.stride(1) != 1:
+        raise KernelError(f"latent_prepare: dkv {tuple(dkv.shape)} holds no {rank} + {rot_dim} values per row")
+    _need(c_weight, "latent norm weight", torch.float32, (rank,))
+    _need(inv_freq, "inv_freq", torch.float32, (rot_dim // 2,))
+    _need(cache, "cache", q.dtype, (None, 1, None, rank + rot_dim))
+    _need(page_table, "page_table", torch.int32, (None, None))
+    _check(_fn("latent", "zk_latent_prepare")(
+        _ptr(q), _ptr(q_full), _ptr(dkv), dkv.stride(0), _ptr(c_weight), _ptr(inv_freq), _ptr(cache), _ptr(tok_seq),
+        _ptr(tok_pos), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n, n_heads, dim, rot_dim, rank, eps,
+        cache.shape[2], 1 if write_kv else 0, dtype_code(q.dtype), _ptr(status), _stream()), "latent_prepare")
+
+
+def head_gemm(a: torch.Tensor, a_head: int, w: torch.Tensor, out: torch.Tensor, o_head: int,
+              gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t, h * o_head + n] = sum_k a[t, h * a_head + k] * w[h, n, k] for every head h, times
+    sigmoid(gate[t, h]) if `gate` (float32 [tokens, >= H], may be a view of wider rows) is given.
+    a [tokens, >= H * a_head], out [tokens, >= H * o_head] in the run dtype; w [H, N, K] contiguous, K <= a_head,
+    N <= o_head."""
+    _need(w, "w", (torch.float32, torch.bfloat16), (None, None, None))
+    H, N, K = w.shape
+    _need(a, "a", w.dtype, (None, None))
+    _need(out, "out", w.dtype, (a.shape[0], None))
+    if K > a_head or N > o_head or a.shape[1] < H * a_head or out.shape[1] < H * o_head:
+        raise KernelError(f"head_gemm: a {tuple(a.shape)} / w {tuple(w.shape)} / out {tuple(out.shape)} do not fit heads "
+                          f"of {a_head} inputs and {o_head} outputs")
+    ld_gate = 0
+    if gate is not None:
+        _need(gate, "gate", torch.float32, (a.shape[0], None), contiguous=False)
+        if gate.shape[1] < H or gate.stride(1) != 1:
+            raise KernelError(f"head_gemm: gate {tuple(gate.shape)} holds no {H} values per row")
+        ld_gate = gate.stride(0)
+    _check(_fn("latent", "zk_head_gemm")(_ptr(a), a.stride(0), a_head, _ptr(w), _ptr(out), out.stride(0), o_head, _ptr(gate),
+                                         ld_gate, a.shape[0], H, N, K, dtype_code(w.dtype), _stream()), "head_gemm")
     return out
 
 
@@ -942,10 +1072,12 @@ def qk_prepare(qkv, k_cache, v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos, seq_
 
 
 def qk_prepare_span(qkv, k_cache, v_cache, q_w, k_w, tok_seq, tok_pos, seq_slot, page_table, n_heads: int, n_kv: int,
-                    head_dim: int, value_dim: int, eps: float, status, write_kv: bool = True) -> torch.Tensor:
-    """RMSNorm of q over all its heads at once (weight [H*hd], or None) and of k likewise ([Hkv*hd]),
-    no rotation; q out as [n, H*hd]; k and v (value_dim wide) written to their pages.  A row of qkv
-    holds [q | k | v], or q alone with write_kv False (the caches are then only needed for their sizes)."""
+                    head_dim: int, value_dim: int, eps: float, status, write_kv: bool = True,
+                    inv_freq: Optional[torch.Tensor] = None, n_rot: int = 0) -> torch.Tensor:
+    """RMSNorm of q over all its heads at once (weight [H*hd], or None) and of k likewise ([Hkv*hd]); with
+    `inv_freq` [n_rot / 2] the first n_rot entries of every q and k head are then rotated by the token's position
+    (entry i paired with entry i + n_rot/2); q out as [n, H*hd]; k and v (value_dim wide) written to their pages.
+    A row of qkv holds [q | k | v], or q alone with write_kv False (the caches are then only needed for their sizes)."""
     qd, kd, vd = n_heads * head_dim, n_kv * head_dim, n_kv * value_dim
     _need(qkv, "qkv", (torch.float32, torch.bfloat16), (None, qd + (kd + vd if write_kv else 0)))
     n = qkv.shape[0]
@@ -956,11 +1088,16 @@ def qk_prepare_span(qkv, k_cache, v_cache, q_w, k_w, tok_seq, tok_pos, seq_slot,
     if k_w is not None:
         _need(k_w, "k norm weight", torch.float32, (kd,))
     _need(page_table, "page_table", torch.int32, (None, None))
+    if inv_freq is not None:
+        if n_rot <= 0 or n_rot % 2 or n_rot > head_dim:
+            raise KernelError(f"qk_prepare_span: the rotated width {n_rot} must be even and at most head_dim {head_dim}")
+        _need(inv_freq, "inv_freq", torch.float32, (n_rot // 2,))
     q = torch.empty((n, qd), dtype=qkv.dtype, device=qkv.device)
     _check(_fn("attention", "zk_qk_prepare_span")(
         _ptr(qkv), qkv.stride(0), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(q_w), _ptr(k_w), _ptr(tok_seq),
         _ptr(tok_pos), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n, n_heads, n_kv, head_dim, value_dim,
-        eps, k_cache.shape[2], 1 if write_kv else 0, dtype_code(qkv.dtype), _ptr(status), _stream()), "qk_prepare_span")
+        eps, k_cache.shape[2], 1 if write_kv else 0, dtype_code(qkv.dtype), _ptr(status), _ptr(inv_freq), int(n_rot),
+        _stream()), "qk_prepare_span")
     return q
 
 
@@ -1010,13 +1147,15 @@ def _takes(lib: str, fn: str, n_heads: int, n_kv: int, head_dim: int, page_size:
 @functools.lru_cache(maxsize=None)      # a pure function of sizes, asked for by every attention layer of every step
 def attention_plan(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, page_size: int,
                    single_token: bool, window: int = 0, value_dim: Optional[int] = None,
-                   biased: bool = False, talking: bool = False) -> tuple[str, int]:
+                   biased: bool = False, talking: bool = False, extras: bool = False) -> tuple[str, int]:
     """Which attention kernel runs for these sizes and how many tokens its query tiles hold:
     ("single_token_tc" | "single_token" | "prompt_tc5" | "prompt_tc" | "general", tokens per tile).
     Values of another width than the keys go to the general kernel; a distance bias on the scores is
     taken by the general kernel and the two mma.sync kernels ("prompt_tc", "single_token_tc"); weights that
     are mixed across the heads after the softmax (`talking`) by those three and the tcgen05 prompt kernel."""
     same_width = value_dim is None or value_dim == head_dim
+    if extras:          # kept first tokens, a sink, values read from the key rows: the general kernel's
+        return "general", attn_tile_shape(n_heads, n_kv)[0]
     if same_width and dtype == torch.bfloat16 and n_heads % n_kv == 0:
         if (not single_token and window <= 0 and not biased and _may_take("attention_prefill_tc5", n_heads, n_kv, head_dim, page_size)
                 and _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_takes")(n_heads, n_kv, head_dim, page_size, window)):
@@ -1033,8 +1172,13 @@ def attention_plan(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, p
 def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table, n_heads: int, n_kv: int,
               head_dim: int, scale: float, window: int = 0, num_splits: int = 1, split_keys: int = 0,
               single_token: bool = False, kind: Optional[str] = None, value_dim: Optional[int] = None,
-              bias: Optional[tuple] = None, talk: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Causal grouped-query attention of a packed batch against the paged cache.  With
+              bias: Optional[tuple] = None, talk: Optional[torch.Tensor] = None, keep_first: int = 0,
+              sink: Optional[torch.Tensor] = None, values_in_keys: bool = False) -> torch.Tensor:
+    """Causal grouped-query attention of a packed batch against the paged cache.
+    `keep_first`: with a window, the first so many positions of a sequence stay visible to every later query.
+    `sink` float32 [H]: exp(sink_h) is one more term of head h's softmax denominator (no key, no value, not scaled).
+    `values_in_keys`: there is no value cache; a value row is the first `value_dim` entries of the key row.
+    All three are the general kernel's.  With
     num_splits > 1 the keys are cut at multiples of `split_keys` and merged afterwards.
     `single_token` says that every sequence brings exactly one query (row b = sequence b); the
     bfloat16 kernels for that case are used when they take the sizes.  `kind` names the kernel as
@@ -1049,7 +1193,18 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     n = q.shape[0]
     vd = head_dim if value_dim is None else int(value_dim)
     _need(k_cache, "k_cache", q.dtype, (None, n_kv, None, head_dim))
-    _need(v_cache, "v_cache", q.dtype, (None, n_kv, None, vd))
+    if values_in_keys:
+        if vd > head_dim or talk is not None:
+            raise KernelError("attention: values read from the key rows are at most as wide as the keys, and no weights "
+                              "are mixed across heads")
+        v_cache = k_cache
+    else:
+        _need(v_cache, "v_cache", q.dtype, (None, n_kv, None, vd))
+    extras = keep_first > 0 or sink is not None or values_in_keys
+    if extras and kind not in (None, "general"):
+        raise KernelError(f"attention: the '{kind}' kernel takes no kept first tokens, sink or values in the key rows")
+    if sink is not None:
+        _need(sink, "sink", torch.float32, (n_heads,))
     if bias is not None:
         for b, nm in zip(bias, ("bias r1", "bias r2")):
             _need(b, nm, torch.float32, (n_heads,))
@@ -1072,7 +1227,8 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     bq, gc = attn_tile_shape(n_heads, n_kv)
     n_tiles = tile_seq.numel()
     out = torch.empty((n, n_heads * vd), dtype=q.dtype, device=q.device)
-    if vd != head_dim or (talk is not None and kind != "single_token_tc") or (bias is not None and kind != "single_token_tc"):
+    if (vd != head_dim or extras or (talk is not None and kind != "single_token_tc")
+            or (bias is not None and kind != "single_token_tc")):
         single_token = False        # the general kernel runs single tokens as tiles of one query
     part_o = part_ml = None
     value_heads = n_kv if talk is not None else 1
@@ -1112,7 +1268,7 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
             return _merge_talk(part_o, part_ml, talk, out, n, n_heads, n_kv, vd, num_splits)
         if num_splits > 1:
             _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, head_dim,
-                                                     num_splits, dtype_code(q.dtype), _stream()), "attention merge")
+                                                     num_splits, dtype_code(q.dtype), None, n_heads, _stream()), "attention merge")
         return out
     if kind == "single_token_tc":
         raise KernelError("attention: the tensor-core single-token kernel does not take these sizes")
@@ -1124,19 +1280,20 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
             scale, num_splits, split_keys, _stream()), "attention (single token)")
         if num_splits > 1:
             _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, head_dim,
-                                                     num_splits, dtype_code(q.dtype), _stream()), "attention merge")
+                                                     num_splits, dtype_code(q.dtype), None, n_heads, _stream()), "attention merge")
         return out
     _check(_fn("attention", "zk_attn_fwd")(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tile_seq), _ptr(tile_q0),
         _ptr(cu_q), _ptr(seq_start), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n_tiles, n, n_heads, n_kv,
         head_dim, page_size, window, scale, bq, gc, num_splits, split_keys, dtype_code(q.dtype), vd, r1, r2,
-        1 if talk is not None else 0, _stream()),
+        1 if talk is not None else 0, int(keep_first), _ptr(sink), 1 if values_in_keys else 0, _stream()),
         "attention")
     if talk is not None:
         return _merge_talk(part_o, part_ml, talk, out, n, n_heads, n_kv, vd, num_splits)
     if num_splits > 1:
         _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, vd,
-                                                 num_splits, dtype_code(q.dtype), _stream()), "attention merge")
+                                                 num_splits, dtype_code(q.dtype), _ptr(sink), n_heads, _stream()),
+               "attention merge")
     return out
 
 

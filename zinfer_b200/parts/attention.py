@@ -19,6 +19,9 @@ position i and key position j, in float32, before the softmax.  `unit_norm_after
 heads are divided by their root mean square (no weight, the layer's eps) after the position encoding.
 `talk_name`: a matrix T [heads, heads]; after the softmax head h's weights become
 sum_g T[h, g] * (weights of head g), and head h applies them to the values of its own key/value head.
+`keep_first` (with a window): the first so many tokens of a sequence stay visible to every later query, at their
+true positions; the cache keeps their pages.  `sink_name`: one learned number per head, [heads]; exp(sink_h) is
+one more term of head h's softmax denominator, with no key and no value, and is not scaled.
 
 How the kernels are launched is decided here, not by the engine: the table of query tiles of a
 step, and for single-token steps the cut of a sequence's keys into chunks that separate blocks
@@ -91,7 +94,8 @@ class GqaAttention(Mixer):
                  norm_eps: float = 1e-5, position: Optional[PositionEncoding] = None, window: int = 0,
                  scale: Optional[float] = None, split_keys: int = 0, value_dim: Optional[int] = None,
                  qk_norm_span: str = "head", distance_bias: Optional[tuple[str, str]] = None, own_kv: bool = True,
-                 unit_norm_after_rotation: bool = False, talk_name: Optional[str] = None):
+                 unit_norm_after_rotation: bool = False, talk_name: Optional[str] = None, keep_first: int = 0,
+                 sink_name: Optional[str] = None):
         """split_keys: keys per chunk of single-token attention, a multiple of 64 (0 = chosen per
         step from the batch and the GPU's size)."""
         if n_heads % n_kv_heads:
@@ -100,11 +104,18 @@ class GqaAttention(Mixer):
             raise ValueError(f"qk_norm_span {qk_norm_span!r}: 'head' or 'all'")
         self.value_dim = head_dim if value_dim is None else int(value_dim)
         self.qk_norm_span, self.distance_bias, self.own_kv = qk_norm_span, distance_bias, bool(own_kv)
-        # the kernel that prepares q and k over the whole projection has no rotation
+        # the kernel that prepares q and k over the whole projection takes a rotation table, no other encoding
         self.span_prepare = qk_norm_span == "all" or not own_kv
-        if self.span_prepare and (position is not None or unit_norm_after_rotation):
-            raise ValueError("attention: a position encoding and a norm behind it go with per-head norms and key/value "
-                             "weights of the mixer's own")
+        if self.span_prepare and unit_norm_after_rotation:
+            raise ValueError("attention: a norm behind the position encoding goes with per-head norms")
+        if self.span_prepare and position is not None and not own_kv:
+            raise ValueError("attention: a position encoding goes with key/value weights of the mixer's own")
+        if keep_first < 0 or (keep_first > 0 and window <= 0):
+            raise ValueError("attention: kept first tokens go with a window")
+        if (keep_first > 0 or sink_name is not None) and (talk_name is not None or distance_bias is not None):
+            raise ValueError("attention: no kernel takes kept first tokens or a sink together with a distance bias or "
+                             "weights mixed across heads")
+        self.keep_first, self.sink_name, self.sink = int(keep_first), sink_name, None
         if self.span_prepare and qk_norm_span == "head" and (q_norm_name or k_norm_name):
             raise ValueError("attention: per-head norms go with key/value weights of the mixer's own")
         if talk_name is not None and distance_bias is not None:
@@ -154,6 +165,8 @@ class GqaAttention(Mixer):
             specs += [WeightSpec(n, (self.n_heads,), role="vector", init="abs_normal") for n in self.distance_bias]
         if self.talk_name is not None:
             specs.append(WeightSpec(self.talk_name, (self.n_heads, self.n_heads), role="vector"))
+        if self.sink_name is not None:
+            specs.append(WeightSpec(self.sink_name, (self.n_heads,), role="vector"))
         return specs
 
     def load(self, weights, dtype, device):
@@ -167,11 +180,12 @@ class GqaAttention(Mixer):
         if self.distance_bias is not None:
             self.bias_r1, self.bias_r2 = (weights[n] for n in self.distance_bias)
         self.talk = weights[self.talk_name] if self.talk_name is not None else None
+        self.sink = weights[self.sink_name].contiguous() if self.sink_name is not None else None
         self._sm_count = kernels.sm_count(device) if torch.device(device).type == "cuda" else 0
 
     def kv_request(self):
         return KVRequest(self.n_kv, self.head_dim, self.window,
-                         None if self.value_dim == self.head_dim else self.value_dim)
+                         None if self.value_dim == self.head_dim else self.value_dim, keep_first=self.keep_first)
 
     def check(self, dtype, page_size):
         most = kernels.attn_max_head_dim()
@@ -198,8 +212,13 @@ class GqaAttention(Mixer):
         common = dict(tok_seq=ctx.tok_seq, tok_pos=ctx.tok_pos, seq_slot=ctx.seq_slot, page_table=kv.page_table,
                       n_heads=self.n_heads, n_kv=self.n_kv, head_dim=self.head_dim, eps=self.eps, status=ctx.status)
         if self.span_prepare:
+            if self.position is not None and rot is None:
+                raise ValueError("attention: norms over the whole projection take a rotation table, no other encoding")
+            if rot is not None and rot.interleaved:
+                raise ValueError("attention: norms over the whole projection take the half-split pairing only")
             q = kernels.qk_prepare_span(qkv, kv.k, kv.v, self.q_norm, self.k_norm, value_dim=self.value_dim,
-                                        write_kv=call.writes_kv, **common)
+                                        write_kv=call.writes_kv, inv_freq=rot.inv_freq if rot else None,
+                                        n_rot=rot.n_rot if rot else 0, **common)
         elif fused:
             q = kernels.qk_prepare(qkv, kv.k, kv.v, self.q_norm, self.k_norm, rot.inv_freq if rot else None,
                                    n_rot=rot.n_rot if rot else 0, interleaved=rot.interleaved if rot else False,
@@ -217,7 +236,8 @@ class GqaAttention(Mixer):
                                    write_kv=call.writes_kv, unit_norm_after=self.unit_norm_after, **common)
         kind, tile_tokens = kernels.attention_plan(q.dtype, self.n_heads, self.n_kv, self.head_dim, kv.page_size,
                                                    ctx.is_decode, self.window, self.value_dim,
-                                                   self.distance_bias is not None, self.talk_name is not None)
+                                                   self.distance_bias is not None, self.talk_name is not None,
+                                                   self.keep_first > 0 or self.sink is not None)
         tile_seq, tile_q0 = ctx.memo(("query tiles", tile_tokens), lambda: self._tiles_on_device(ctx, tile_tokens))
         num_splits, split_keys = (key_chunks(ctx.n_seqs, self.n_kv, ctx.max_kv_len, self._sm_count, self.split_keys)
                                   if ctx.is_decode else (1, 0))
@@ -226,7 +246,7 @@ class GqaAttention(Mixer):
                                 num_splits, split_keys, single_token=ctx.is_decode, kind=kind,
                                 value_dim=self.value_dim,
                                 bias=(self.bias_r1, self.bias_r2) if self.distance_bias is not None else None,
-                                talk=self.talk)
+                                talk=self.talk, keep_first=self.keep_first, sink=self.sink)
         linear(att, self.w_out, out=out, accumulate=accumulate)
 
 

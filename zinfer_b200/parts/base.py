@@ -68,12 +68,14 @@ class KVRequest:
     values in a first tensor ("k") and `n_kv_heads` rows of `value_dim` values in a second ("v").
     value_dim None = as wide as head_dim (keys and values of attention); value_dim 0 = no
     second tensor (a mixer that keeps one vector per token, e.g. a latent).
-    window = 0 keeps every token; window = W lets the cache drop tokens more than W behind."""
+    window = 0 keeps every token; window = W lets the cache drop tokens more than W behind, except the first
+    `keep_first` tokens of the sequence, which stay for good."""
 
     n_kv_heads: int
     head_dim: int
     window: int = 0
     value_dim: Optional[int] = None
+    keep_first: int = 0
 
     @property
     def v_dim(self) -> int:

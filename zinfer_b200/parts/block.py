@@ -138,5 +138,44 @@ class SublayerNormBlock(Block):
             self.ffn_norm.add_normed(ctx, m, x)
 
 
+class ParallelBlock(Block):
+    """x += Mixer(norm(x)) + FFN(norm(x)): ONE norm, both sublayers read its output, both results are summed into
+    the float32 rows (the mixer's first, then the feed-forward's).  `ffn` None: the mixer alone.  The normalised rows
+    are made once, before the mixer changes the rows they are made from, and both sublayers read that tensor."""
+
+    def __init__(self, norm: Norm, mixer: Mixer, ffn: FeedForward | None = None):
+        self.norm, self.mixer, self.ffn = norm, mixer, ffn
+
+    def parts(self):
+        return [p for p in (self.norm, self.mixer, self.ffn) if p is not None]
+
+    def entry_norm(self):
+        return self.norm
+
+    def forward(self, ctx, call, x):
+        self.forward_chained(ctx, call, x)
+
+    def forward_chained(self, ctx, call, x, entry=None, next_norm=None):
+        consumers = [p for p in (self.mixer, self.ffn) if p is not None]
+        h = None
+        if all(getattr(p, "takes_pending_norm", False) for p in consumers):
+            h = self.norm.pending(ctx, x) if entry is None else self.norm.pending(ctx, x, entry)
+        if h is None:
+            h = self.norm.forward(ctx, x)
+        if self.ffn is None:
+            last = ahead_for(self.mixer, next_norm, ctx, x)
+            self.mixer.forward(ctx, call, h, x if last is None else last, True)
+            return last
+        # The mixer sums into the rows that the norm reads: what the feed-forward reads must exist before it does.
+        # (A pending norm is evaluated when its first consumer wants it, which may be never for a fused kernel.)
+        if hasattr(h, "tensor"):
+            h.tensor()
+        self.mixer.forward(ctx, call, h, x, True)
+        last = ahead_for(self.ffn, next_norm, ctx, x)
+        self.ffn.forward(ctx, h, x if last is None else last, True)
+        return last
+
+
+BLOCKS.register("parallel", ParallelBlock)
 BLOCKS.register("prenorm", PreNormBlock)
 BLOCKS.register("sublayer_norm", SublayerNormBlock)

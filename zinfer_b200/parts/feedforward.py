@@ -57,6 +57,26 @@ class SwiGLU(FeedForward):
         linear(h, self.w_down, out=out, accumulate=accumulate)
 
 
+class ClampedGLU(SwiGLU):
+    """Gated feed-forward whose gate is capped from above and whose linear branch is clamped and shifted by one:
+
+        g = min(xn W_gate^T, limit),  u = clamp(xn W_up^T, -limit, limit),  h = g * sigmoid(alpha * g) * (u + 1),
+        out (+)= h W_down^T
+
+    `limit` and `alpha` are constructor parameters; the unit is evaluated in float32.  Weights are stacked as in `SwiGLU`."""
+
+    def __init__(self, hidden: int, ffn_dim: int, gate_name: str, up_name: str, down_name: str, limit: float,
+                 alpha: float = 1.702):
+        super().__init__(hidden, ffn_dim, gate_name, up_name, down_name)
+        if not limit > 0:
+            raise ValueError(f"clamped GLU: the limit must be positive, got {limit}")
+        self.limit, self.alpha = float(limit), float(alpha)
+
+    def forward(self, ctx, xn, out, accumulate):
+        h = kernels.clamped_glu(linear(xn, self.w_gate_up), self.limit, self.alpha, self.interleave)
+        linear(h, self.w_down, out=out, accumulate=accumulate)
+
+
 class ActMlp(FeedForward):
     """Ungated feed-forward: out (+)= act(xn W_up^T) W_down^T, act one of `kernels.ACTIVATIONS`
     ("gelu" is the exact erf form), evaluated in float32."""
@@ -83,3 +103,4 @@ class ActMlp(FeedForward):
 
 FEED_FORWARDS.register("swiglu", SwiGLU)
 FEED_FORWARDS.register("act_mlp", ActMlp)
+FEED_FORWARDS.register("clamped_glu", ClampedGLU)

@@ -35,6 +35,26 @@ from .linear import FUSION_GROUP, interleave_rows
 GROUPED_MIN_TOKENS = 96
 
 
+def expert_rows(experts: np.ndarray, n_experts: int, top: int, tile: int = 1):
+    """For the expert of every (token, k) pair, flat in the order t * top + k: (row_token [rows]: the token of each
+    row when the pairs are sorted by expert, keeping their order within an expert, -1 for a padding row; pair_row
+    [n * top]: the row each pair went to; bounds [experts + 1]: expert e owns rows bounds[e] .. bounds[e + 1]).
+    Every expert's rows are padded to a multiple of `tile`."""
+    order = np.argsort(experts, kind="stable")
+    counts = np.bincount(experts, minlength=n_experts)
+    padded = -(-counts // tile) * tile
+    bounds = np.zeros(n_experts + 1, dtype=np.int64)
+    np.cumsum(padded, out=bounds[1:])
+    starts = np.zeros(n_experts, dtype=np.int64)
+    np.cumsum(counts[:-1], out=starts[1:])
+    rows = np.arange(order.size) + np.repeat(bounds[:-1] - starts, counts)     # row of each pair, in sorted order
+    row_token = np.full(int(bounds[-1]), -1, dtype=np.int32)
+    row_token[rows] = order // top
+    pair_row = np.empty(order.size, dtype=np.int32)
+    pair_row[order] = rows
+    return row_token, pair_row, bounds
+
+
 class TableMoE(FeedForward):
     takes_residual_rows = True       # the shared expert's gate reads the float32 rows
 
@@ -117,19 +137,7 @@ class TableMoE(FeedForward):
         if ids.size and (ids.min() < 0 or ids.max() >= self.vocab):
             ids = np.clip(ids, 0, self.vocab - 1)            # a bad id is flagged by the embedding kernel
         experts = self.table_sort_keys[ids].reshape(-1)      # 8- or 16-bit keys: NumPy sorts those by radix, ten times faster
-        order = np.argsort(experts, kind="stable")
-        counts = np.bincount(experts, minlength=self.n_experts)
-        padded = -(-counts // tile) * tile
-        bounds = np.zeros(self.n_experts + 1, dtype=np.int64)
-        np.cumsum(padded, out=bounds[1:])
-        starts = np.zeros(self.n_experts, dtype=np.int64)
-        np.cumsum(counts[:-1], out=starts[1:])
-        rows = np.arange(order.size) + np.repeat(bounds[:-1] - starts, counts)     # row of each pair, in sorted order
-        row_token = np.full(int(bounds[-1]), -1, dtype=np.int32)
-        row_token[rows] = order // self.top
-        pair_row = np.empty(order.size, dtype=np.int32)
-        pair_row[order] = rows
-        return row_token, pair_row, bounds
+        return expert_rows(experts, self.n_experts, self.top, tile)
 
     def _upload(self, words: np.ndarray, device) -> torch.Tensor:
         """int32 words on the device, copied through the part's own pinned buffer (rewritten only after the
@@ -148,20 +156,26 @@ class TableMoE(FeedForward):
         self._staged.record()
         return dev
 
-    def _expert_by_expert(self, ctx, rows, host_tokens, out, accumulate):
+    def _expert_by_expert(self, ctx, rows, host_tokens, out, accumulate, chosen=None, weights=None):
+        """`chosen` (host, flat [n * top]) names the experts when a router picked them, `weights` (device, float32
+        [n, top]) their weights; without them the table decides and every expert weighs 1/top."""
         tile = kernels.GEMM_TC_GROUP_ROWS
         grouped = (self.interleave and rows.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.ffn_dim % 8 == 0
                    and rows.is_contiguous())
 
         def make():
-            row_token, pair_row, bounds = self.routing(host_tokens, tile if grouped else 1)
+            if chosen is None:
+                row_token, pair_row, bounds = self.routing(host_tokens, tile if grouped else 1)
+            else:
+                row_token, pair_row, bounds = expert_rows(chosen, self.n_experts, self.top, tile if grouped else 1)
             tile_group = np.repeat(np.arange(self.n_experts), np.diff(bounds) // tile).astype(np.int32) if grouped \
                 else np.zeros(0, dtype=np.int32)
             sizes = np.cumsum([row_token.size, pair_row.size, tile_group.size])
             dev = self._upload(np.concatenate([row_token, pair_row, tile_group]), ctx.device)
             return dev[:sizes[0]], dev[sizes[0]:sizes[1]], dev[sizes[1]:sizes[2]], bounds
 
-        row_token, pair_row, tile_group, bounds = ctx.memo(("expert rows", id(self)), make)
+        # a table's rows depend on the step's ids alone; a router's on what this very call read
+        row_token, pair_row, tile_group, bounds = ctx.memo(("expert rows", id(self)), make) if chosen is None else make()
         xg = kernels.moe_gather(rows, row_token)
         if grouped:
             h = kernels.gemm_tc_grouped(xg, self.w_gate_up, tile_group, swiglu=True)
@@ -172,7 +186,58 @@ class TableMoE(FeedForward):
                 r0, r1 = int(bounds[e]), int(bounds[e + 1])
                 if r1 > r0:
                     ff.forward(ctx, xg[r0:r1], y[r0:r1], False)
-        kernels.moe_combine(y, pair_row, self.top, out, accumulate)
+        kernels.moe_combine(y, pair_row, self.top, out, accumulate, weights)
+
+
+class RoutedMoE(TableMoE):
+    """Mixture of small gated feed-forwards picked by a learned router:
+
+        z = W_router x_t (float32),  s = softmax(z) over all experts,  the `top` largest s are chosen,
+        y_t = sum_k (s_k / (sum of the chosen s + 1e-20)) * W_down[e_k] (silu(W_gate[e_k] x_t) * (W_up[e_k] x_t))
+
+    The router runs on the device (`kernels.moe_router`: ids and weights per token).  Few tokens: the two
+    weight-streaming kernels read them there, so a single-token step needs nothing from the host and can be
+    recorded.  Many tokens (prompt steps): the chosen ids come to the host once per call, the rows are sorted by
+    expert there and the grouped tensor-core contractions of `TableMoE` run them."""
+
+    takes_residual_rows = False
+    takes_pending_norm = True
+
+    def __init__(self, hidden: int, ffn_dim: int, n_experts: int, top: int, router_name: str, expert_names):
+        super().__init__(hidden, ffn_dim, n_experts, top, 1, "", expert_names)
+        self.router_name, self.w_router = router_name, None
+
+    def weight_specs(self):
+        F, D = self.ffn_dim, self.hidden
+        specs = [WeightSpec(self.router_name, (self.n_experts, D), role="vector")]      # kept in float32
+        for g, u, d in self.names:
+            specs += [WeightSpec(g, (F, D)), WeightSpec(u, (F, D)), WeightSpec(d, (D, F))]
+        return specs
+
+    def load(self, weights, dtype, device):
+        self.w_router = weights[self.router_name].contiguous()
+        stack = (lambda g, u: interleave_rows([g, u])) if self.interleave else (lambda g, u: torch.cat([g, u], dim=0))
+        self.w_gate_up = torch.stack([stack(weights[g], weights[u]) for g, u, _ in self.names]).contiguous()
+        self.w_down = torch.stack([weights[d] for _, _, d in self.names]).contiguous()
+        self.experts = []
+        for e in range(self.n_experts):
+            ff = SwiGLU(self.hidden, self.ffn_dim, "", "", "")
+            ff.w_gate_up, ff.w_down = self.w_gate_up[e], self.w_down[e]
+            self.experts.append(ff)
+
+    def forward(self, ctx, xn, out, accumulate):
+        from .linear import as_tensor
+        rows = as_tensor(xn)
+        if rows.dtype != ctx.dtype:
+            rows = kernels.cast_rows(rows, ctx.dtype)
+        ids, wts = kernels.moe_router(rows, self.w_router, self.top)
+        if ctx.is_decode or rows.shape[0] < GROUPED_MIN_TOKENS:
+            kernels.moe_routed(rows, ids, wts, self.w_gate_up, self.interleave, self.w_down, ctx.status, out=out,
+                               accumulate=accumulate)
+            return
+        chosen = ids.cpu().numpy().reshape(-1).astype(np.int64)
+        self._expert_by_expert(ctx, rows, None, out, accumulate, chosen=np.clip(chosen, 0, self.n_experts - 1), weights=wts)
 
 
 FEED_FORWARDS.register("table_moe", TableMoE)
+FEED_FORWARDS.register("routed_moe", RoutedMoE)
