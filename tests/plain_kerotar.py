@@ -118,15 +118,20 @@ def clamped_glu(h, W, limit):
     return (g * sigmoid(1.702 * g) * (u + 1.0)) @ W["down"].T
 
 
-def routed_experts(h, W, experts, top):
-    """Softmax router over all experts, the `top` largest taken, their scores renormalised."""
+def routed_experts(h, W, experts, top, margins=None):
+    """Softmax router over all experts, the `top` largest taken, their scores renormalised.  `margins` (a list of
+    n numbers, or None) is lowered, per token, to the gap between the last chosen logit and the first one left out,
+    relative to the largest |logit|: how close the choice came to falling the other way."""
     n = h.shape[0]
     out = np.zeros((n, W["e0.down"].shape[0]))
     for t in range(n):
         z = W["router"] @ h[t]
         s = np.exp(z - z.max())
         s = s / s.sum()
-        chosen = sorted(range(experts), key=lambda i: (-s[i], i))[:top]
+        order = sorted(range(experts), key=lambda i: (-s[i], i))
+        chosen = order[:top]
+        if margins is not None and top < experts:
+            margins[t] = min(margins[t], float(z[order[top - 1]] - z[order[top]]) / float(np.abs(z).max()))
         total = sum(s[i] for i in chosen) + 1e-20
         for i in chosen:
             g, u = W[f"e{i}.gate"] @ h[t], W[f"e{i}.up"] @ h[t]
@@ -138,7 +143,7 @@ def sub(weights, prefix):
     return {k[len(prefix):]: v for k, v in weights.items() if k.startswith(prefix)}
 
 
-def layer(x, weights, i, L, eps, pos0=0):
+def layer(x, weights, i, L, eps, pos0=0, margins=None):
     """One parallel layer: both sublayers read the same normalised rows, x + mixer + feed-forward."""
     h = rmsnorm(x, weights[f"l{i}.norm1"], eps)
     Wm = sub(weights, f"l{i}.mix.")
@@ -154,7 +159,7 @@ def layer(x, weights, i, L, eps, pos0=0):
         if mlp["kind"] == "dense":
             y = y + clamped_glu(h, Wf, mlp["limit"])
         elif mlp["kind"] == "moe":
-            y = y + routed_experts(h, Wf, mlp["router"]["experts"], mlp["router"]["top"])
+            y = y + routed_experts(h, Wf, mlp["router"]["experts"], mlp["router"]["top"], margins)
         else:
             raise ValueError(mlp["kind"])
     return x + y
@@ -171,8 +176,9 @@ def run_order(cfg):
     return runs + [(i, None) for i in range(lp["stop"], n)]
 
 
-def forward(cfg, weights, tokens, taps=None):
-    """Logits [n, vocab] of one whole sequence; `taps` (a list) receives the rows after every layer run."""
+def forward(cfg, weights, tokens, taps=None, margins=None):
+    """Logits [n, vocab] of one whole sequence; `taps` (a list) receives the rows after every layer run; `margins`
+    (a list of n numbers) is lowered to every token's closest expert choice (see routed_experts)."""
     weights = {k: np.asarray(v, dtype=np.float64) for k, v in weights.items()}
     eps = cfg["norm"]["eps"]
     x0 = weights["embed"][np.asarray(tokens)] * cfg.get("embedding", {}).get("scale", 1.0)
@@ -180,7 +186,7 @@ def forward(cfg, weights, tokens, taps=None):
     for i, t in run_order(cfg):
         if t is not None:
             x = np.concatenate([x, x0], axis=1) @ weights["loop.in"].T + weights["loop.step"][t]
-        x = layer(x, weights, i, cfg["layers"][i], eps)
+        x = layer(x, weights, i, cfg["layers"][i], eps, margins=margins)
         if taps is not None:
             taps.append(x.copy())
     return rmsnorm(x, weights["final.norm"], eps) @ weights["head"].T

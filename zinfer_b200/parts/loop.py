@@ -31,7 +31,7 @@ class PassInput(Part):
     def __init__(self, step_name: str, passes: int, width: int, starts: Mapping[int, int], in_name: str | None = None):
         """starts: schedule index of a pass's first entry -> the pass's number."""
         self.step_name, self.passes, self.width = step_name, int(passes), int(width)
-        self.in_name, self.w_rows, self.w_emb = in_name, None, None
+        self.in_name, self.w_rows, self.w_emb, self._emb = in_name, None, None, None
         self.starts = {int(c): int(t) for c, t in starts.items()}
         if any(not 0 <= t < self.passes for t in self.starts.values()):
             raise ValueError(f"pass numbers {sorted(self.starts.values())} outside the {self.passes} passes")
@@ -65,8 +65,10 @@ class PassInput(Part):
             return
         from .linear import linear
         rows = kernels.cast_rows(x, ctx.dtype) if ctx.dtype != x.dtype else kernels.weighted_sum(x.unsqueeze(0), None, 1, torch.empty_like(x))
-        emb = ctx.memo(("embedding rows in the run dtype", id(self)),
-                       lambda: kernels.cast_rows(x_emb, ctx.dtype) if ctx.dtype != x_emb.dtype else x_emb)
+        # the embedding's rows in the run dtype, made once per step (every pass reads the same rows)
+        if self._emb is None or self._emb[0] is not x_emb:
+            self._emb = (x_emb, kernels.cast_rows(x_emb, ctx.dtype) if ctx.dtype != x_emb.dtype else x_emb)
+        emb = self._emb[1]
         linear(rows, self.w_rows, out=x)                  # x is overwritten: `rows` is a copy of it
         linear(emb, self.w_emb, out=x, accumulate=True)
         kernels.rows_add(x, self.step[t])
