@@ -296,11 +296,59 @@ def lfm2_like_zosurax(sz: dict) -> dict:
                 block_auto_adjust_ff_dim=False)
 
 
-COMPARISONS = {"ponusun": (PONUSUN_SIZES, ponusun_config, lfm2_like), "zosurax": (ZOSURAX_SIZES, zosurax_config, lfm2_like_zosurax)}
+# Kerotar beside the closest existing architecture at equal size, Ponusun without its convolutions, shared experts,
+# borrowed keys and logit cap: width, layers, vocabulary, the heads and window of the windowed layers, the dense
+# feed-forwards' hidden units and the experts are the same.  Kerotar's even layers attend through a latent (Ponusun:
+# windowed attention there too), its windowed layers keep a sequence's first tokens and have a sink, its router is
+# learned (Ponusun: a table by token id), and one norm feeds both sublayers of a layer.
+KEROTAR_SIZES = {
+    "w1024": dict(width=1024, layers=8, heads=16, kv=4, dim=64, window=512, keep=4, lat_dim=64, lat_rot=32, lat_vdim=64,
+                  kv_rank=256, q_rank=512, experts=16, top=2, ff=1024, dense_ff=4096, vocab=32768),
+    "w2048": dict(width=2048, layers=8, heads=32, kv=8, dim=64, window=1024, keep=4, lat_dim=64, lat_rot=32, lat_vdim=64,
+                  kv_rank=512, q_rank=768, experts=16, top=2, ff=2048, dense_ff=8192, vocab=65536),
+}
+
+
+def kerotar_config(sz: dict) -> dict:
+    layers = []
+    for i in range(sz["layers"]):
+        if i % 2 == 0:
+            kind = "latent_attention"
+            mixer = {"heads": sz["heads"], "dim": sz["lat_dim"], "rot_dim": sz["lat_rot"], "vdim": sz["lat_vdim"],
+                     "kv_rank": sz["kv_rank"], "q_rank": sz["q_rank"], "scale": (sz["lat_dim"] + sz["lat_rot"]) ** -0.5,
+                     "rot": {"base": 10000.0, "dims": sz["lat_rot"]}}
+            mlp = {"kind": "dense", "ff": sz["dense_ff"], "limit": 7.0}
+        else:
+            kind = "attention"
+            mixer = {"heads": sz["heads"], "kv_heads": sz["kv"], "dim": sz["dim"], "vdim": sz["dim"], "scale": sz["dim"] ** -0.5,
+                     "rot": {"base": 10000.0, "dims": sz["dim"] // 2}, "mask": {"size": sz["window"], "keep_first": sz["keep"]}}
+            mlp = {"kind": "moe", "expert": {"ff": sz["ff"]}, "router": {"experts": sz["experts"], "top": sz["top"]}}
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Kerotar", "vocab": sz["vocab"], "width": sz["width"], "max_positions": CONTEXT,
+            "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "layers": layers}
+
+
+def ponusun_like_kerotar(sz: dict) -> dict:
+    layers = []
+    for i in range(sz["layers"]):
+        mixer = {"heads": sz["heads"], "kv_heads": sz["kv"], "dim": sz["dim"], "vdim": sz["dim"], "scale": sz["dim"] ** -0.5,
+                 "mask": {"size": sz["window"]}}
+        mlp = ({"kind": "dense", "ff": sz["dense_ff"]} if i % 2 == 0 else
+               {"kind": "moe", "expert": {"ff": sz["ff"]}, "router": {"experts": sz["experts"], "top": sz["top"]}})
+        layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Ponusun", "vocab": sz["vocab"], "width": sz["width"], "max_positions": CONTEXT,
+            "norm": {"eps": 1e-5}, "layers": layers}
+
+
+# new architecture -> (sizes, its configuration, the configuration of the architecture beside it, that one's name)
+COMPARISONS = {"ponusun": (PONUSUN_SIZES, ponusun_config, lfm2_like, "lfm2"),
+               "zosurax": (ZOSURAX_SIZES, zosurax_config, lfm2_like_zosurax, "lfm2"),
+               "kerotar": (KEROTAR_SIZES, kerotar_config, ponusun_like_kerotar, "ponusun")}
 
 
 def ponusun_arm(args) -> dict:
-    """Prompt and single-token throughput of Ponusun (or Zosurax, `--model zosurax`) and of LFM2 at equal size, random
+    """Prompt and single-token throughput of Ponusun (or Zosurax, Kerotar: `--model`) and of the closest earlier
+    architecture (LFM2; for Kerotar, Ponusun) at equal size, random
     weights, bfloat16: one prompt of --prefill-tokens tokens in one step (median of 5), then --steps single-token
     steps of --batch sequences replayed from CUDA graphs (prompts of 512..2,048 tokens)."""
     import numpy as np
@@ -310,8 +358,9 @@ def ponusun_arm(args) -> dict:
 
     kernels.require_cuda()
     new = args.model
-    sizes, new_config, like_config = COMPARISONS[new]
-    out = {"metric": f"prompt and single-token tokens/s, {new.capitalize()} beside LFM2 at equal size (random weights)", "unit": "tokens/s",
+    sizes, new_config, like_config, like = COMPARISONS[new]
+    like_title = {"lfm2": "LFM2"}.get(like, like.capitalize())
+    out = {"metric": f"prompt and single-token tokens/s, {new.capitalize()} beside {like_title} at equal size (random weights)", "unit": "tokens/s",
            "dtype": "bf16", "data": "synthetic", "steps": args.steps, "warmup": args.warmup, "batch": args.batch,
            "prefill_tokens": args.prefill_tokens, "sizes": {}}
     wanted = [args.size] if args.size else list(sizes)
@@ -319,7 +368,7 @@ def ponusun_arm(args) -> dict:
         for name in wanted:
             sz = sizes[name]
             row = {}
-            for arch, cfg_dict in ((new, new_config(sz)), ("lfm2", like_config(sz))):
+            for arch, cfg_dict in ((new, new_config(sz)), (like, like_config(sz))):
                 if args.arch and arch != args.arch:
                     continue
                 cfg = z.config_from_dict(cfg_dict)
@@ -352,8 +401,8 @@ def ponusun_arm(args) -> dict:
                 row[arch] = res
                 del engine, model
                 torch.cuda.empty_cache()
-            if new in row and "lfm2" in row:
-                row[f"{new}_over_lfm2"] = {k: round(row[new][k]["tokens_per_s"] / row["lfm2"][k]["tokens_per_s"], 3)
+            if new in row and like in row:
+                row[f"{new}_over_{like}"] = {k: round(row[new][k]["tokens_per_s"] / row[like][k]["tokens_per_s"], 3)
                                            for k in row[new]}
             out["sizes"][name] = dict(row, config={k: sz[k] for k in sz})
     out["clocks"] = clocks.summary()
@@ -461,12 +510,12 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="with --only prefill: the prompt's length (the headline line always uses 2,048)")
-    ap.add_argument("--model", default="1.2b", choices=["1.2b", "ponusun", "zosurax"] + sorted(SECONDARY),
-                    help="1.2b: the headline benchmark; 2.6b, 350m: the secondary workloads (decode only); ponusun, zosurax: "
-                         "that architecture beside LFM2 at equal size, prompt and single-token steps")
-    ap.add_argument("--size", default="", choices=[""] + sorted(PONUSUN_SIZES), help="with --model ponusun or zosurax: one size only")
-    ap.add_argument("--arch", default="", choices=["", "ponusun", "zosurax", "lfm2"],
-                    help="with --model ponusun or zosurax: one architecture only")
+    ap.add_argument("--model", default="1.2b", choices=["1.2b", "ponusun", "zosurax", "kerotar"] + sorted(SECONDARY),
+                    help="1.2b: the headline benchmark; 2.6b, 350m: the secondary workloads (decode only); ponusun, zosurax, "
+                         "kerotar: that architecture beside the closest earlier one at equal size, prompt and single-token steps")
+    ap.add_argument("--size", default="", choices=[""] + sorted(PONUSUN_SIZES), help="with --model ponusun, zosurax or kerotar: one size only")
+    ap.add_argument("--arch", default="", choices=["", "ponusun", "zosurax", "kerotar", "lfm2"],
+                    help="with --model ponusun, zosurax or kerotar: one architecture of the two only")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":

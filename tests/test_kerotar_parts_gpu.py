@@ -227,6 +227,19 @@ def test_one_marked_key_decides_or_is_out_of_sight(k, dtype, H, G, d, page, mark
     scale), while the values come from the second half.  A marked key in sight decides the output; one out of sight
     (behind the kept tokens, before the window) must not move it at all.  The last token comes in a prompt step, and
     then as a single token behind a prompt."""
+    marked_key(k, dtype, H, G, d, page, mark, seen, T_MARK, WINDOW, KEEP, (T_MARK, T_MARK - 1, 150))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("mark,seen", [(0, True), (63, True), (64, True), (69, True), (70, False), (128, False), (519, False),
+                                       (520, True), (575, True), (576, True)])
+def test_kept_keys_over_a_tile_border_far_behind_the_window(k, dtype, mark, seen):
+    """600 tokens, a window of 80 and 70 kept tokens (more than a key tile of 64), pages of 64: the kept keys and the
+    window lie in different pages, tiles and chunks of the keys, in a prompt step and in single-token steps."""
+    marked_key(k, dtype, 4, 2, 64, 64, mark, seen, 600, 80, 70, (600, 599, 560))
+
+
+def marked_key(k, dtype, H, G, d, page, mark, seen, T_MARK, WINDOW, KEEP, prompts):
     D, vd, T = 2 * d, d, T_MARK
     t = window_tensors(D, H, G, d, vd, dtype, 90, split=True)
     t["q"] = t["k"].reshape(G, 1, d, D).expand(G, H // G, d, D).reshape(H * d, D).clone()
@@ -245,7 +258,7 @@ def test_one_marked_key_decides_or_is_out_of_sight(k, dtype, H, G, d, page, mark
         assert np.abs(ref[-1] - moved[-1]).max() > 0.1 * np.abs(ref).max(), "the marked key does not decide the last query"
     else:
         assert np.abs(ref[-1] - moved[-1]).max() == 0.0
-    for prompt in (T, T - 1, 150):
+    for prompt in prompts:
         outs = run_mixer(k, mixer, dtype, [x], [prompt], page=page)
         close(outs[0], ref, dtype, f"prompt of {prompt}")
 
@@ -300,6 +313,10 @@ def plain_latent(x, t, H, d, p, e, r, s, scale, base, eps=2e-6):
     (128, 8, 32, 16, 32, 320, 96, 0.1, 1000.0, 32),           # a latent wider than 256: rows of 336 values
     (64, 2, 16, 8, 16, 32, 40, 2.5, 100.0, 16),               # scores so sharp that one or two far keys decide a query
     (128, 4, 32, 32, 64, 64, 64, 1.5, 10000.0, 64),
+    (128, 4, 48, 16, 40, 96, 64, 0.12, 10000.0, 64),          # values narrower than the kernel's value rows
+    (128, 2, 64, 32, 64, 160, 64, 0.1, 10000.0, 64),          # keys of 96 entries in rows of 128, values of 64
+    (128, 2, 96, 32, 128, 160, 64, 0.09, 10000.0, 128),       # keys and values of 128
+    (128, 3, 32, 16, 96, 80, 64, 0.14, 500.0, 64),            # values wider than the keys
 ])
 def test_latent_attention_alone(k, dtype, D, H, d, p, e, r, s, scale, base, page):
     t = latent_tensors(D, H, d, p, e, r, s, dtype, 70)

@@ -79,7 +79,7 @@ class Bench:
         self.cache.sync()
         buf = torch.from_numpy(pack_batch(slots, starts, [[0] * n for n in lens])).to(self.dev)
         ctx = StepContext(self.dtype, self.dev, self.status, buf, sum(lens), len(slots), lens,
-                          max(s + n for s, n in zip(starts, lens)))
+                          max(s + n for s, n in zip(starts, lens)), from_start=all(s == 0 for s in starts))
         return ctx
 
     def done(self, slots, rows_per_seq):
@@ -92,7 +92,8 @@ def run_mixer(k, mixer, dtype, xs, prompt_lens, page=16):
     in one packed step, the rest one row per sequence and step; shorter sequences leave the batch
     earlier.  Slots are taken in reverse so that slot and batch index differ.  Returns out[b]
     [T_b, D] (float32, the mixer's own output without a residual)."""
-    bench = Bench(k, mixer, dtype, n_slots=len(xs) + 1, page=page)
+    longest = max(x.shape[0] for x in xs)
+    bench = Bench(k, mixer, dtype, n_slots=len(xs) + 1, max_seq=max(256, -(-longest // page) * page), page=page)
     held = bench.cache.alloc_slots(len(xs) + 1)
     slots = held[1:][::-1]
     D = xs[0].shape[1]

@@ -72,7 +72,11 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
                           const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
                           const int* __restrict__ page_table, int pt_stride, int n_seqs, int H, int Hkv, int page_size,
                           int window, float scale, int num_splits, int split_keys, const float* __restrict__ bias_r1,
-                          const float* __restrict__ bias_r2, int cross) {
+                          const float* __restrict__ bias_r2, int cross, int keep, const float* __restrict__ sink) {
+  // keep: with a window, the first `keep` keys of a sequence stay visible; the block whose chunk starts at the
+  // window's lower edge also walks the tiles that hold them, before its own.
+  // sink [H]: exp(sink_h) is one more term of head h's softmax denominator (no key, no value, unscaled); it enters
+  // where the result is normalised, here with one chunk, in the merge kernel with several.
   // cross: blockIdx.y also counts the key/value heads whose VALUES a block reads in place of its own
   // key/value head's, and the unnormalised sums always go to part_o / part_ml, rows ordered
   // (split, sequence, head, value head): for a kernel that mixes the heads' weights after the softmax.
@@ -116,7 +120,11 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
     }
 
   const int k_begin = (c0 / DT_TK) * DT_TK;
-  const int n_tiles = c1 > c0 ? (c1 - k_begin + DT_TK - 1) / DT_TK : 0;
+  // kept first keys [0, a_hi) lie below this block's first tile when its chunk starts at the window's edge
+  const int keep_here = (keep > 0 && c0 == lo && c1 > c0) ? keep : 0;
+  const int a_hi = min(keep_here, k_begin);
+  const int a_tiles = (a_hi + DT_TK - 1) / DT_TK;
+  const int n_tiles = c1 > c0 ? a_tiles + (c1 - k_begin + DT_TK - 1) / DT_TK : 0;
 
   // A thread's 16-byte pieces of a tile: piece n is row r0 + n * ROWS_STEP, chunk ch0.  The swizzle
   // depends on the row only through its low three bits, which ROWS_STEP (a multiple of 8) leaves
@@ -128,18 +136,24 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
 
   // Tiles are loaded in order, so where the next one lies (entry of the page table, place in the page)
   // is carried along: no division per tile.
-  int ld_kb = k_begin, ld_entry = k_begin / page_size, ld_in_page = k_begin % page_size;
+  int ld_kb = a_tiles > 0 ? 0 : k_begin, ld_entry = ld_kb / page_size, ld_in_page = ld_kb % page_size;
   auto load_tile = [&](int buf) {
     const int kb = ld_kb;
     const int page = pt[ld_entry];
     const size_t base = (((size_t)(page < 0 ? 0 : page) * Hkv + kvh) * page_size + ld_in_page) * HD;
+    const int stop = kb < a_hi ? a_hi : c1;  // the kept keys' tiles end at a_hi
     ld_kb += DT_TK;
     ld_in_page += DT_TK;
     if (ld_in_page == page_size) {
       ld_in_page = 0;
       ++ld_entry;
     }
-    if (page >= 0 && kb + DT_TK <= c1) {     // a whole tile: nothing to test per piece
+    if (kb < a_hi && ld_kb >= a_hi) {        // behind the kept keys' last tile comes the chunk's first
+      ld_kb = k_begin;
+      ld_entry = k_begin / page_size;
+      ld_in_page = k_begin % page_size;
+    }
+    if (page >= 0 && kb + DT_TK <= stop) {   // a whole tile: nothing to test per piece
       const bf16* kg = k_cache + base + g_off0;
       const bf16* vg = v_rows + base + g_off0;
       unsigned char* ks = Ksm(buf) + sm_off0;
@@ -152,7 +166,7 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
     } else {
       for (int i = tid; i < DT_TK * CH; i += DT_WARPS * 32) {
         const int r = i / CH, ch = i % CH;
-        const bool valid = page >= 0 && kb + r < c1;
+        const bool valid = page >= 0 && kb + r < stop;
         const size_t off = base + (size_t)(valid ? r : 0) * HD + ch * 8;
         cp_async16(Ksm(buf) + swz<HD>(r, ch), k_cache + off, valid);
         cp_async16(Vsm(buf) + swz<HD>(r, ch), v_rows + off, valid);
@@ -194,7 +208,7 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
     else cp_async_commit();
     cp_async_wait<NST - 1>();
     __syncthreads();
-    const int kb = k_begin + t * DT_TK + 16 * warp;   // this warp's 16 keys of the tile
+    const int kb = (t < a_tiles ? t * DT_TK : k_begin + (t - a_tiles) * DT_TK) + 16 * warp;   // this warp's 16 keys of the tile
 
     // S = Q K^T: 2 key groups of 8, KS k steps
     float s[2][4];
@@ -224,7 +238,7 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
         float sc = s[j][i] * scale2;
         if (biased) sc -= r1_2[i >> 1] * log1pf(r2[i >> 1] * (float)max(L - 1 - kp, 0));
         if (edge_tile) {
-          const bool vis = kp >= c0 && kp < c1;
+          const bool vis = (kp >= c0 || kp < keep_here) && kp < c1;
           s[j][i] = vis ? sc : -INFINITY;
         } else {
           s[j][i] = sc;
@@ -316,6 +330,12 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
     }
     const int head = kvh * G + h;
     if (num_splits == 1 && !cross) {
+      if (sink) {
+        const float sk = sink[head], m_fin = fmaxf(M, sk);
+        const float back = M == -INFINITY ? 0.f : expf(M - m_fin);
+        Lsum = Lsum * back + expf(sk - m_fin);
+        O *= back;
+      }
       out[(size_t)b * H * HD + (size_t)head * HD + d] = __float2bfloat16_rn(Lsum > 0.f ? O / Lsum : 0.f);
     } else {
       const size_t row = cross ? (((size_t)split * n_seqs + b) * H + head) * Hkv + vh : ((size_t)split * n_seqs + b) * H + head;
@@ -332,7 +352,7 @@ template <int HD, int NST>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_ml,
            const int* seq_start, const int* seq_slot, const int* page_table, int pt_stride, int n_seqs, int H, int Hkv,
            int page_size, int window, float scale, int num_splits, int split_keys, const float* r1, const float* r2,
-           int cross, cudaStream_t stream) {
+           int cross, int keep, const float* sink, cudaStream_t stream) {
   auto kern = attn_decode_tc_kernel<HD, NST>;
   const size_t smem = 2 * NST * (size_t)DT_TK * HD * 2;
   static_assert(2 * NST * DT_TK * HD * 2 >= (2 * DT_WARPS * 16 + DT_WARPS * 16 * HD) * 4, "the merge fits in the tile buffers");
@@ -343,7 +363,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
   dim3 grid(n_seqs, Hkv * (cross ? Hkv : 1), num_splits);
   return zk_launch_dependent(kern, grid, dim3(DT_WARPS * 32), smem, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out,
                                               part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H, Hkv,
-                                              page_size, window, scale, num_splits, split_keys, r1, r2, cross);
+                                              page_size, window, scale, num_splits, split_keys, r1, r2, cross, keep, sink);
   return ZK_LAUNCH_STATUS();
 }
 
@@ -360,12 +380,15 @@ int zk_attn_decode_tc_takes(int H, int Hkv, int hd, int page_size) {
   return (hd == 64 || hd == 128) && G >= 1 && G <= 16 && page_size % DT_TK == 0;
 }
 
-// q, out [n_seqs, H*hd] bfloat16; partials as for zk_attn_fwd when num_splits > 1.
+// q, out [n_seqs, H*hd] bfloat16; partials as for zk_attn_fwd when num_splits > 1 (the merge then adds the sink).
+// keep > 0 (with a window) and sink [H] float32 as the kernel describes them; neither goes with the cross mode.
 int zk_attn_decode_tc(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_ml,
                       const int* seq_start, const int* seq_slot, const int* page_table, int pt_stride, int n_seqs, int H,
                       int Hkv, int hd, int page_size, int window, float scale, int num_splits, int split_keys,
-                      const float* bias_r1, const float* bias_r2, int cross, cudaStream_t stream) {
+                      const float* bias_r1, const float* bias_r2, int cross, int keep, const float* sink,
+                      cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
+  if (keep < 0 || (keep > 0 && window <= 0) || (cross && (keep > 0 || sink))) return ZK_EINVAL;
   if (cross && (!part_o || !part_ml)) return ZK_EINVAL;
   if (!zk_attn_decode_tc_takes(H, Hkv, hd, page_size) || num_splits < 1) return ZK_EINVAL;
   if ((bias_r1 == nullptr) != (bias_r2 == nullptr)) return ZK_EINVAL;
@@ -379,12 +402,12 @@ int zk_attn_decode_tc(const void* q, const void* k_cache, const void* v_cache, v
   const bool short_chunks = num_splits > 1 && split_keys <= 4 * DT_TK;
   if (hd == 64 && short_chunks)
     return launch<64, 4>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
-                         Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, cross, stream);
+                         Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, cross, keep, sink, stream);
   if (hd == 64)
     return launch<64, 2>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
-                         Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, cross, stream);
+                         Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, cross, keep, sink, stream);
   return launch<128, 2>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
-                     Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, cross, stream);
+                     Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, cross, keep, sink, stream);
 }
 
 }  // extern "C"

@@ -53,15 +53,22 @@ __device__ __forceinline__ int swz(int r, int ch) {
   return r * (HD * 2) + ((ch & ~7) | ((ch ^ r) & 7)) * 16;
 }
 
-// HD: head_dim, 64 or 128 (rows of a tile are whole 128-byte lines, which the swizzle assumes).  GP: heads of a KV group packed into one block.
-template <int HD, int GP>
+// HD: head_dim, 64 or 128 (rows of a tile are whole 128-byte lines, which the swizzle assumes).  HDV: width of a
+// value row, 64 or 128.  GP: heads of a KV group packed into one block.
+template <int HD, int HDV, int GP>
 __global__ void __launch_bounds__(PF_WARPS * 32)
     attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         bf16* __restrict__ out, const int* __restrict__ tile_seq, const int* __restrict__ tile_q0,
                         const int* __restrict__ cu_q, const int* __restrict__ seq_start,
                         const int* __restrict__ seq_slot, const int* __restrict__ page_table, int pt_stride, int H,
                         int Hkv, int page_size, int window, float scale, const float* __restrict__ bias_r1,
-                        const float* __restrict__ bias_r2, float* __restrict__ part_o, float* __restrict__ part_ml) {
+                        const float* __restrict__ bias_r2, float* __restrict__ part_o, float* __restrict__ part_ml,
+                        int keep, const float* __restrict__ sink) {
+  // keep: with a window, the first `keep` positions of a sequence stay visible to every later query; the tiles
+  // that hold them and lie below the window's reach are walked before the window's.
+  // sink [H]: exp(sink_h) is one more term of head h's softmax denominator (no key, no value, unscaled).
+  // page_table null: the keys and values are no cache but rows laid out like one for this step alone, sequence b's
+  // positions from page seq_slot[b] on, one page after the other.
   // bias_r1, bias_r2 [H] (both or neither): r1_h * ln(1 + r2_h * (i - j)) is taken off the scaled score of
   // query position i and key position j, in float32, before the softmax.
   // part_o, part_ml (both or neither): the cross mode.  blockIdx.z names a key/value head whose VALUES this
@@ -71,10 +78,11 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
   constexpr int BQ = PF_ROWS / GP;          // tokens per block
   constexpr int KS = HD / 16;               // k steps of Q K^T
   constexpr int CH = HD / 8;                // 16-byte chunks per row
-  constexpr int TILE_BYTES = PF_TK * HD * 2;
+  constexpr int CHV = HDV / 8;
+  constexpr int TILE_BYTES = PF_TK * HD * 2, VTILE_BYTES = PF_TK * HDV * 2;
   extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* Ksm[2] = {smem, smem + 2 * TILE_BYTES};
-  unsigned char* Vsm[2] = {smem + TILE_BYTES, smem + 3 * TILE_BYTES};
+  unsigned char* Ksm[2] = {smem, smem + TILE_BYTES};
+  unsigned char* Vsm[2] = {smem + 2 * TILE_BYTES, smem + 2 * TILE_BYTES + VTILE_BYTES};
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;
@@ -88,7 +96,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
   const int b = tile_seq[tile], q0 = tile_q0[tile];
   const int t_base = cu_q[b], Tq = cu_q[b + 1] - t_base;
   const int start = seq_start[b];
-  const int* pt = page_table + (size_t)seq_slot[b] * pt_stride;
+  const int* pt = page_table ? page_table + (size_t)seq_slot[b] * pt_stride : nullptr;
+  const int page0 = seq_slot[b];
 
   // this thread's two rows: r0 = warp*16 + g and r0 + 8
   int row_tok[2], row_head[2], row_hi[2], row_lo[2];
@@ -132,27 +141,34 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
     k_begin = first_hi > window ? first_hi - window : 0;
   }
   k_begin = (k_begin / PF_TK) * PF_TK;
-  const int n_tiles = (k_end - k_begin + PF_TK - 1) / PF_TK;
+  // kept first tokens below the window's first tile: keys [0, a_hi) in a_tiles tiles, which end at or before k_begin
+  const int a_hi = (keep > 0 && k_begin > 0) ? min(keep, k_begin) : 0;
+  const int a_tiles = (a_hi + PF_TK - 1) / PF_TK;
+  const int n_tiles = a_tiles + (k_end - k_begin + PF_TK - 1) / PF_TK;
 
   auto load_tile = [&](int t, int buf) {
-    const int kb = k_begin + t * PF_TK;
-    const int page = pt[kb / page_size];
+    const int kb = t < a_tiles ? t * PF_TK : k_begin + (t - a_tiles) * PF_TK;
+    const int k_stop = t < a_tiles ? a_hi : k_end;
+    const int page = pt ? pt[kb / page_size] : page0 + kb / page_size;
     const size_t base = (((size_t)(page < 0 ? 0 : page) * Hkv + kvh) * page_size + kb % page_size) * HD;
-    const size_t vbase = (((size_t)(page < 0 ? 0 : page) * Hkv + vh) * page_size + kb % page_size) * HD;
+    const size_t vbase = (((size_t)(page < 0 ? 0 : page) * Hkv + vh) * page_size + kb % page_size) * HDV;
     for (int i = tid; i < PF_TK * CH; i += PF_WARPS * 32) {
       const int r = i / CH, ch = i % CH;
-      const bool valid = page >= 0 && kb + r < k_end;
-      const size_t off = (size_t)(valid ? r : 0) * HD + ch * 8;
-      cp_async16(Ksm[buf] + swz<HD>(r, ch), k_cache + base + off, valid);
-      cp_async16(Vsm[buf] + swz<HD>(r, ch), v_cache + vbase + off, valid);
+      const bool valid = page >= 0 && kb + r < k_stop;
+      cp_async16(Ksm[buf] + swz<HD>(r, ch), k_cache + base + (size_t)(valid ? r : 0) * HD + ch * 8, valid);
+    }
+    for (int i = tid; i < PF_TK * CHV; i += PF_WARPS * 32) {
+      const int r = i / CHV, ch = i % CHV;
+      const bool valid = page >= 0 && kb + r < k_stop;
+      cp_async16(Vsm[buf] + swz<HDV>(r, ch), v_cache + vbase + (size_t)(valid ? r : 0) * HDV + ch * 8, valid);
     }
     cp_async_commit();
   };
 
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  float o[HD / 8][4];
+  float o[HDV / 8][4];
 #pragma unroll
-  for (int j = 0; j < HD / 8; ++j)
+  for (int j = 0; j < HDV / 8; ++j)
 #pragma unroll
     for (int i = 0; i < 4; ++i) o[j][i] = 0.f;
 
@@ -166,7 +182,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
       cp_async_wait<0>();
     }
     __syncthreads();
-    const int kb = k_begin + t * PF_TK;
+    const int kb = t < a_tiles ? t * PF_TK : k_begin + (t - a_tiles) * PF_TK;
 
     // S = Q K^T: 8 key groups of 8, KS k steps
     float s[8][4];
@@ -195,7 +211,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
       for (int i = 0; i < 4; ++i) {
         const int h = i >> 1;
         const int kp = kb + 8 * j + 2 * c + (i & 1);
-        const bool vis = row_ok[h] && kp >= row_lo[h] && kp < row_hi[h];
+        const bool vis = row_ok[h] && (kp >= row_lo[h] || kp < keep) && kp < row_hi[h];
         float sc = s[j][i] * scale;
         if (biased && vis) sc -= r1[h] * log1pf(r2[h] * (float)(row_hi[h] - 1 - kp));
         s[j][i] = vis ? sc : -INFINITY;
@@ -225,14 +241,14 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
       m_run[h] = m_new[h];
     }
 #pragma unroll
-    for (int j = 0; j < HD / 8; ++j) {
+    for (int j = 0; j < HDV / 8; ++j) {
       o[j][0] *= alpha[0];
       o[j][1] *= alpha[0];
       o[j][2] *= alpha[1];
       o[j][3] *= alpha[1];
     }
 
-    // O += P V: 4 key steps of 16, HD/8 column groups (two per ldmatrix)
+    // O += P V: 4 key steps of 16, HDV/8 column groups (two per ldmatrix)
 #pragma unroll
     for (int kk = 0; kk < PF_TK / 16; ++kk) {
       unsigned pa[4];
@@ -241,10 +257,10 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
       pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
       pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
-      for (int jn = 0; jn < HD / 8; jn += 2) {
+      for (int jn = 0; jn < HDV / 8; jn += 2) {
         unsigned bfr[4];
         const int r = 16 * kk + (lane & 7) + ((lane >> 3) & 1) * 8, ch = jn + (lane >> 4);
-        ldmatrix_x4_trans(bfr, Vsm[buf] + swz<HD>(r, ch));
+        ldmatrix_x4_trans(bfr, Vsm[buf] + swz<HDV>(r, ch));
         mma16816(o[jn], pa, bfr[0], bfr[1]);
         mma16816(o[jn + 1], pa, bfr[2], bfr[3]);
       }
@@ -257,28 +273,35 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
     if (!row_ok[h]) continue;
     if (cross) {
       const size_t row = ((size_t)row_tok[h] * H + row_head[h]) * Hkv + vh;
-      float* dst = part_o + row * HD;
+      float* dst = part_o + row * HDV;
 #pragma unroll
-      for (int j = 0; j < HD / 8; ++j)
+      for (int j = 0; j < HDV / 8; ++j)
         *reinterpret_cast<float2*>(dst + 8 * j + 2 * c) = make_float2(o[j][2 * h], o[j][2 * h + 1]);
       if (c == 0) *reinterpret_cast<float2*>(part_ml + row * 2) = make_float2(m_run[h], l_run[h]);
       continue;
     }
-    const float inv = l_run[h] > 0.f ? 1.0f / l_run[h] : 0.f;
-    bf16* dst = out + (size_t)row_tok[h] * H * HD + (size_t)row_head[h] * HD;
+    float back = 1.f;                                // what the sums are scaled by when the sink raises the maximum
+    if (sink) {
+      const float sk = sink[row_head[h]];
+      const float m_fin = fmaxf(m_run[h], sk);
+      back = m_run[h] == -INFINITY ? 0.f : expf(m_run[h] - m_fin);
+      l_run[h] = l_run[h] * back + expf(sk - m_fin);
+    }
+    const float inv = l_run[h] > 0.f ? back / l_run[h] : 0.f;
+    bf16* dst = out + (size_t)row_tok[h] * H * HDV + (size_t)row_head[h] * HDV;
 #pragma unroll
-    for (int j = 0; j < HD / 8; ++j)
+    for (int j = 0; j < HDV / 8; ++j)
       *reinterpret_cast<unsigned*>(dst + 8 * j + 2 * c) = pack_bf16(o[j][2 * h] * inv, o[j][2 * h + 1] * inv);
   }
 }
 
-template <int HD, int GP>
+template <int HD, int HDV, int GP>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq, const int* tile_q0,
            const int* cu_q, const int* seq_start, const int* seq_slot, const int* page_table, int pt_stride, int n_tiles,
            int H, int Hkv, int page_size, int window, float scale, const float* r1, const float* r2, float* part_o,
-           float* part_ml, cudaStream_t stream) {
-  auto kern = attn_prefill_kernel<HD, GP>;
-  const size_t smem = 4 * (size_t)PF_TK * HD * 2;
+           float* part_ml, int keep, const float* sink, cudaStream_t stream) {
+  auto kern = attn_prefill_kernel<HD, HDV, GP>;
+  const size_t smem = 2 * (size_t)PF_TK * (HD + HDV) * 2;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -286,7 +309,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, c
   dim3 grid(n_tiles, Hkv * ((H / Hkv) / GP), part_o ? Hkv : 1);
   kern<<<grid, PF_WARPS * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out,
                                               tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table, pt_stride, H,
-                                              Hkv, page_size, window, scale, r1, r2, part_o, part_ml);
+                                              Hkv, page_size, window, scale, r1, r2, part_o, part_ml, keep, sink);
   return ZK_LAUNCH_STATUS();
 }
 
@@ -308,25 +331,33 @@ int zk_attn_prefill_takes(int H, int Hkv, int hd, int page_size) {
 }
 int zk_attn_prefill_tile_tokens(int H, int Hkv) { return PF_ROWS / packed_heads(H / Hkv); }
 
-// q, out [n_tokens, H*hd] bfloat16; tiles of zk_attn_prefill_tile_tokens tokens.  part_o [n_tokens*H*Hkv, hd] and
+// q [n_tokens, H*hd], out [n_tokens, H*vd] bfloat16 (vd: width of a value row, hd or, with hd 128, 64); tiles of zk_attn_prefill_tile_tokens tokens.  part_o [n_tokens*H*Hkv, hd] and
 // part_ml [n_tokens*H*Hkv, 2] float32 (both or neither) switch the cross mode on: `out` is then not written.
+// keep > 0 (with a window) and sink [H] float32 as the kernel describes them; neither goes with the cross mode.
+// page_table null: keys and values laid out for this step alone, as the kernel describes (seq_slot = first pages).
 int zk_attn_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq,
                     const int* tile_q0, const int* cu_q, const int* seq_start, const int* seq_slot,
-                    const int* page_table, int pt_stride, int n_tiles, int H, int Hkv, int hd, int page_size,
-                    int window, float scale, const float* bias_r1, const float* bias_r2, float* part_o, float* part_ml,
-                    cudaStream_t stream) {
+                    const int* page_table, int pt_stride, int n_tiles, int H, int Hkv, int hd, int vd,
+                    int page_size, int window, float scale, const float* bias_r1, const float* bias_r2, float* part_o, float* part_ml,
+                    int keep, const float* sink, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (!zk_attn_prefill_takes(H, Hkv, hd, page_size) || ((bias_r1 == nullptr) != (bias_r2 == nullptr))) return ZK_EINVAL;
   if ((part_o == nullptr) != (part_ml == nullptr) || (part_o && Hkv > 65535)) return ZK_EINVAL;
+  if (keep < 0 || (keep > 0 && window <= 0) || (part_o && (keep > 0 || sink))) return ZK_EINVAL;
+  if (vd != hd && !(hd == 128 && vd == 64)) return ZK_EINVAL;
   const int gp = packed_heads(H / Hkv);
-#define ZK_PF(HDV, GPV)                                                                                          \
-  if (hd == HDV && gp == GPV)                                                                                    \
-    return launch<HDV, GPV>(q, k_cache, v_cache, out, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table,  \
+#define ZK_PF(HDK, GPV)                                                                                          \
+  if (hd == HDK && vd == HDK && gp == GPV)                                                                       \
+    return launch<HDK, HDK, GPV>(q, k_cache, v_cache, out, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table,  \
                             pt_stride, n_tiles, H, Hkv, page_size, window, scale, bias_r1, bias_r2, part_o, part_ml,  \
-                            stream);
+                            keep, sink, stream);
   ZK_PF(64, 1) ZK_PF(64, 2) ZK_PF(64, 4) ZK_PF(64, 8)
   ZK_PF(128, 1) ZK_PF(128, 2) ZK_PF(128, 4) ZK_PF(128, 8)
 #undef ZK_PF
+  if (hd == 128 && vd == 64 && gp == 1)      // narrow values: attention whose heads each have keys and values of their own
+    return launch<128, 64, 1>(q, k_cache, v_cache, out, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table,
+                              pt_stride, n_tiles, H, Hkv, page_size, window, scale, bias_r1, bias_r2, part_o, part_ml,
+                              keep, sink, stream);
   return ZK_EINVAL;
 }
 

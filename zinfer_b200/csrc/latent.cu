@@ -9,6 +9,11 @@
 //
 // (1) latent_prepare_kernel: norm of the latent, rotation of the shared key part, cache write; rotation of the
 //     queries' rotated parts into their place behind the r latent-space columns.
+//     A prompt step that starts its sequences (nothing cached before it) is cheaper the other way round: every
+//     head's keys and values ARE expanded for the step's own tokens (one contraction of c against [W_uk; W_uv]),
+//     and (1b) latent_pack_kernel lays queries, keys and values out, padded to the widths the tensor-core prompt
+//     kernel takes, in rows ordered like a cache's pages for this step alone.  The scores then cost d + p
+//     multiplications a key, not r + p.
 // (2) head_gemm_kernel: out[t, h, :] = a[t, h, :] W[h]^T for few tokens, weights streamed once (the two per-head
 //     steps around attention in single-token steps), with an optional sigmoid gate per (token, head).
 #include "common.cuh"
@@ -20,13 +25,15 @@
 // rotated p entries of head h go to q_full[t, h, r .. r + p) (rows of H * (r + p); the first r columns of every
 // head are written by the contraction that follows).  Block (t, 1): the token's cache row from dkv (float32, rows
 // `ld_dkv` apart): [rms(dkv[:r]) * w | rot(dkv[r : r + p])].  Pairs (i, i + p/2), angle = float(pos) * inv_freq[i].
+// q_full null: block (t, 0) has nothing to do.  c_out [n, r] (or null): the normalised latent once more, packed.
 template <typename T>
 __global__ void __launch_bounds__(LAT_THREADS)
     latent_prepare_kernel(const T* __restrict__ q, T* __restrict__ q_full, const float* __restrict__ dkv, int ld_dkv,
                           const float* __restrict__ c_w, const float* __restrict__ inv_freq, T* __restrict__ cache,
                           const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                           const int* __restrict__ seq_slot, const int* __restrict__ page_table, int pt_stride, int H,
-                          int d, int p, int r, float eps, int page_size, int write_kv, int* status) {
+                          int d, int p, int r, float eps, int page_size, int write_kv, int* status,
+                          T* __restrict__ c_out) {
   __shared__ float scratch[32];
   zk_let_next_start();
   zk_wait_prior();
@@ -34,6 +41,7 @@ __global__ void __launch_bounds__(LAT_THREADS)
   const int pos = tok_pos[t];
   const int half = p >> 1;
   if (blockIdx.y == 0) {
+    if (!q_full) return;
     for (int idx = tid; idx < H * half; idx += LAT_THREADS) {
       const int h = idx / half, i = idx - h * half;
       const T* src = q + ((size_t)t * H + h) * (d + p) + d;
@@ -46,6 +54,14 @@ __global__ void __launch_bounds__(LAT_THREADS)
     }
     return;
   }
+  if (!write_kv && !c_out) return;
+  const float* src = dkv + (size_t)t * ld_dkv;
+  float ss = 0.f;
+  for (int i = tid; i < r; i += LAT_THREADS) ss = fmaf(src[i], src[i], ss);
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)r + eps);
+  if (c_out)
+    for (int i = tid; i < r; i += LAT_THREADS) c_out[(size_t)t * r + i] = from_f32<T>((src[i] * scale) * c_w[i]);
   if (!write_kv) return;
   const int page = page_table[(size_t)seq_slot[tok_seq[t]] * pt_stride + pos / page_size];
   if (page < 0) {
@@ -53,11 +69,6 @@ __global__ void __launch_bounds__(LAT_THREADS)
     return;
   }
   T* row = cache + ((size_t)page * page_size + pos % page_size) * (r + p);
-  const float* src = dkv + (size_t)t * ld_dkv;
-  float ss = 0.f;
-  for (int i = tid; i < r; i += LAT_THREADS) ss = fmaf(src[i], src[i], ss);
-  ss = block_sum(ss, scratch);
-  const float scale = 1.0f / sqrtf(ss / (float)r + eps);
   for (int i = tid; i < r; i += LAT_THREADS) row[i] = from_f32<T>((src[i] * scale) * c_w[i]);
   for (int i = tid; i < half; i += LAT_THREADS) {
     const float ang = (float)pos * inv_freq[i];
@@ -65,6 +76,64 @@ __global__ void __launch_bounds__(LAT_THREADS)
     const float u = src[r + i], v = src[r + i + half];
     row[r + i] = from_f32<T>(u * c - v * sn);
     row[r + i + half] = from_f32<T>(u * sn + v * c);
+  }
+}
+
+// One block per token of a prompt step whose sequences start at position 0.  q [n, H * (d + p)] as projected;
+// kvx rows `ld_kvx` apart: [H * d expanded unrotated keys | H * e expanded values]; dkv as above (its last p entries
+// are the shared key part before rotation).  Writes q_pad [n, H * HD] = [q_h[:d] | rot(q_h[d:]) | 0], and, at row
+// (page, h, pos % page_size) with page = seq_page0[sequence] + pos / page_size, k_rows [pages, H, page_size, HD] =
+// [k_h | rot(k_rot) | 0] and v_rows [pages, H, page_size, HDV] = [v_h | 0].
+template <typename T>
+__global__ void __launch_bounds__(LAT_THREADS)
+    latent_pack_kernel(const T* __restrict__ q, const T* __restrict__ kvx, int ld_kvx, const float* __restrict__ dkv,
+                       int ld_dkv, const float* __restrict__ inv_freq, T* __restrict__ q_pad, T* __restrict__ k_rows,
+                       T* __restrict__ v_rows, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                       const int* __restrict__ seq_page0, int H, int d, int p, int e, int r, int HD, int HDV,
+                       int page_size) {
+  extern __shared__ float sh[];     // cos [p/2], sin [p/2], rotated shared key part [p]
+  zk_let_next_start();
+  zk_wait_prior();
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const int pos = tok_pos[t];
+  const int half = p >> 1;
+  float* cs = sh;
+  float* sn = sh + half;
+  float* kr = sh + p;
+  const float* src = dkv + (size_t)t * ld_dkv + r;
+  for (int i = tid; i < half; i += LAT_THREADS) {
+    const float ang = (float)pos * inv_freq[i];
+    const float c = cosf(ang), s = sinf(ang);
+    cs[i] = c;
+    sn[i] = s;
+    const float u = src[i], v = src[i + half];
+    kr[i] = u * c - v * s;
+    kr[i + half] = u * s + v * c;
+  }
+  __syncthreads();
+  const size_t page = (size_t)seq_page0[tok_seq[t]] + pos / page_size;
+  const int in_page = pos % page_size;
+  const T zero = from_f32<T>(0.f);
+  for (int idx = tid; idx < H * HD; idx += LAT_THREADS) {
+    const int h = idx / HD, j = idx - h * HD;
+    const T* qh = q + ((size_t)t * H + h) * (d + p);
+    T qv = zero, kv = zero;
+    if (j < d) {
+      qv = qh[j];
+      kv = kvx[(size_t)t * ld_kvx + (size_t)h * d + j];
+    } else if (j < d + p) {
+      const int i = j - d;
+      if (i < half) qv = from_f32<T>(to_f32(qh[d + i]) * cs[i] - to_f32(qh[d + i + half]) * sn[i]);
+      else qv = from_f32<T>(to_f32(qh[d + i - half]) * sn[i - half] + to_f32(qh[d + i]) * cs[i - half]);
+      kv = from_f32<T>(kr[i]);
+    }
+    q_pad[((size_t)t * H + h) * HD + j] = qv;
+    k_rows[((page * H + h) * page_size + in_page) * HD + j] = kv;
+  }
+  for (int idx = tid; idx < H * HDV; idx += LAT_THREADS) {
+    const int h = idx / HDV, j = idx - h * HDV;
+    v_rows[((page * H + h) * page_size + in_page) * HDV + j] =
+        j < e ? kvx[(size_t)t * ld_kvx + (size_t)H * d + (size_t)h * e + j] : zero;
   }
 }
 
@@ -118,18 +187,39 @@ extern "C" {
 int zk_latent_prepare(const void* q, void* q_full, const float* dkv, int ld_dkv, const float* c_w, const float* inv_freq,
                       void* cache, const int* tok_seq, const int* tok_pos, const int* seq_slot, const int* page_table,
                       int pt_stride, int n_tokens, int H, int d, int p, int r, float eps, int page_size, int write_kv,
-                      int dtype, int* status, cudaStream_t stream) {
+                      int dtype, int* status, void* c_out, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (H <= 0 || d <= 0 || p <= 0 || (p & 1) || r <= 0 || page_size <= 0 || ld_dkv < r + p || !inv_freq || !c_w) return ZK_EINVAL;
   const dim3 grid(n_tokens, 2);
   if (dtype == ZK_F32)
     return zk_launch_dependent(latent_prepare_kernel<float>, grid, dim3(LAT_THREADS), 0, stream, (const float*)q, (float*)q_full,
                                dkv, ld_dkv, c_w, inv_freq, (float*)cache, tok_seq, tok_pos, seq_slot, page_table, pt_stride,
-                               H, d, p, r, eps, page_size, write_kv, status);
+                               H, d, p, r, eps, page_size, write_kv, status, (float*)c_out);
   if (dtype == ZK_BF16)
     return zk_launch_dependent(latent_prepare_kernel<bf16>, grid, dim3(LAT_THREADS), 0, stream, (const bf16*)q, (bf16*)q_full,
                                dkv, ld_dkv, c_w, inv_freq, (bf16*)cache, tok_seq, tok_pos, seq_slot, page_table, pt_stride,
-                               H, d, p, r, eps, page_size, write_kv, status);
+                               H, d, p, r, eps, page_size, write_kv, status, (bf16*)c_out);
+  return ZK_EINVAL;
+}
+
+int zk_latent_pack(const void* q, const void* kvx, int ld_kvx, const float* dkv, int ld_dkv, const float* inv_freq,
+                   void* q_pad, void* k_rows, void* v_rows, const int* tok_seq, const int* tok_pos, const int* seq_page0,
+                   int n_tokens, int H, int d, int p, int e, int r, int HD, int HDV, int page_size, int dtype,
+                   cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (H <= 0 || d <= 0 || p <= 0 || (p & 1) || e <= 0 || r <= 0 || HD < d + p || HDV < e || page_size <= 0 ||
+      ld_dkv < r + p || ld_kvx < H * (d + e))
+    return ZK_EINVAL;
+  const size_t smem = sizeof(float) * 2 * (size_t)p;
+  if (smem > 48 * 1024) return ZK_EINVAL;
+  if (dtype == ZK_F32)
+    return zk_launch_dependent(latent_pack_kernel<float>, dim3(n_tokens), dim3(LAT_THREADS), smem, stream, (const float*)q,
+                               (const float*)kvx, ld_kvx, dkv, ld_dkv, inv_freq, (float*)q_pad, (float*)k_rows,
+                               (float*)v_rows, tok_seq, tok_pos, seq_page0, H, d, p, e, r, HD, HDV, page_size);
+  if (dtype == ZK_BF16)
+    return zk_launch_dependent(latent_pack_kernel<bf16>, dim3(n_tokens), dim3(LAT_THREADS), smem, stream, (const bf16*)q,
+                               (const bf16*)kvx, ld_kvx, dkv, ld_dkv, inv_freq, (bf16*)q_pad, (bf16*)k_rows,
+                               (bf16*)v_rows, tok_seq, tok_pos, seq_page0, H, d, p, e, r, HD, HDV, page_size);
   return ZK_EINVAL;
 }
 

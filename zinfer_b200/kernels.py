@@ -41,7 +41,8 @@ _SIGNATURES = {
         "zk_head_gate": "ppiiiiip",
     },
     "latent": {
-        "zk_latent_prepare": "pppi" + "ppppppp" + "iiiiii" + "f" + "iii" + "pp",
+        "zk_latent_prepare": "pppi" + "ppppppp" + "iiiiii" + "f" + "iii" + "ppp",
+        "zk_latent_pack": "ppipip" + "pppppp" + "iiiiiiiiii" + "p",
         "zk_head_gemm": "piippiipiiiiiip",
     },
     "hgrn2": {
@@ -90,7 +91,7 @@ _SIGNATURES = {
         "zk_attn_decode_noalloc_bytes": "iiii",
     },
     "attention_prefill": {
-        "zk_attn_prefill": "pppppppppp" + "iiiiiiif" + "pp" + "pp" + "p",
+        "zk_attn_prefill": "pppppppppp" + "iiiiiiiif" + "pp" + "pp" + "ip" + "p",
         "zk_attn_prefill_takes": "iiii",
         "zk_attn_prefill_tile_tokens": "ii",
     },
@@ -100,7 +101,7 @@ _SIGNATURES = {
         "zk_attn_prefill_tc5_tile_tokens": "ii",
     },
     "attention_decode_tc": {
-        "zk_attn_decode_tc": "pppppppppiiiiiiifii" + "pp" + "i" + "p",
+        "zk_attn_decode_tc": "pppppppppiiiiiiifii" + "pp" + "i" + "ip" + "p",
         "zk_attn_decode_tc_takes": "iiii",
     },
     "sampling": {
@@ -983,15 +984,19 @@ def moe_routed(x: torch.Tensor, route_ids: torch.Tensor, route_w: torch.Tensor, 
 
 def latent_prepare(q: torch.Tensor, q_full: torch.Tensor, dkv: torch.Tensor, c_weight: torch.Tensor, inv_freq: torch.Tensor,
                    cache: torch.Tensor, tok_seq, tok_pos, seq_slot, page_table, n_heads: int, dim: int, rot_dim: int,
-                   rank: int, eps: float, status, write_kv: bool = True) -> None:
+                   rank: int, eps: float, status, write_kv: bool = True, c_out: Optional[torch.Tensor] = None) -> None:
     """For attention over one latent row per token.  q [n, H * (dim + rot_dim)] (run dtype) as projected; the rotated
     part of every head goes, rotated by the token's position, to q_full[:, h, rank : rank + rot_dim] (q_full
     [n, H * (rank + rot_dim)]).  dkv float32 [n, >= rank + rot_dim] (a view of wider rows is fine): the token's
     cache row becomes [rms(dkv[:rank]) * c_weight | rotated dkv[rank : rank + rot_dim]]; cache is one layer's
-    [pages, 1, page_size, rank + rot_dim]."""
+    [pages, 1, page_size, rank + rot_dim].  q_full None: the queries are left alone.  c_out [n, rank] (run dtype):
+    also receives the normalised latents, packed."""
     _need(q, "q", (torch.float32, torch.bfloat16), (None, n_heads * (dim + rot_dim)))
     n = q.shape[0]
-    _need(q_full, "q_full", q.dtype, (n, n_heads * (rank + rot_dim)))
+    if q_full is not None:
+        _need(q_full, "q_full", q.dtype, (n, n_heads * (rank + rot_dim)))
+    if c_out is not None:
+        _need(c_out, "c_out", q.dtype, (n, rank))
     _need(dkv, "dkv", torch.float32, (n, None), contiguous=False)
     if dkv.shape[1] < rank + rot_dim or dkv.stride(1) != 1:
         raise KernelError(f"latent_prepare: dkv {tuple(dkv.shape)} holds no {rank} + {rot_dim} values per row")
@@ -1002,7 +1007,34 @@ def latent_prepare(q: torch.Tensor, q_full: torch.Tensor, dkv: torch.Tensor, c_w
     _check(_fn("latent", "zk_latent_prepare")(
         _ptr(q), _ptr(q_full), _ptr(dkv), dkv.stride(0), _ptr(c_weight), _ptr(inv_freq), _ptr(cache), _ptr(tok_seq),
         _ptr(tok_pos), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n, n_heads, dim, rot_dim, rank, eps,
-        cache.shape[2], 1 if write_kv else 0, dtype_code(q.dtype), _ptr(status), _stream()), "latent_prepare")
+        cache.shape[2], 1 if write_kv else 0, dtype_code(q.dtype), _ptr(status), _ptr(c_out), _stream()), "latent_prepare")
+
+
+def latent_pack(q: torch.Tensor, kvx: torch.Tensor, dkv: torch.Tensor, inv_freq: torch.Tensor, tok_seq, tok_pos,
+                seq_page0: torch.Tensor, n_pages: int, page_size: int, n_heads: int, dim: int, rot_dim: int, value_dim: int,
+                rank: int, key_width: int, value_width: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Queries, keys and values of a prompt step that starts its sequences, for attention over the step's own rows.
+    q [n, H * (dim + rot_dim)] as projected; kvx [n, H * dim + H * value_dim]: every head's expanded unrotated keys,
+    then every head's values; dkv float32 [n, >= rank + rot_dim] (its entries rank.. are the shared key part before
+    rotation).  Returns q_pad [n, H * key_width] = [q_h[:dim] | rot(q_h[dim:]) | 0], k_rows [n_pages, H, page_size,
+    key_width] = [k_h | rot(k_rot) | 0] and v_rows [n_pages, H, page_size, value_width] = [v_h | 0], a token of
+    sequence b at position pos in page seq_page0[b] + pos // page_size."""
+    _need(q, "q", (torch.float32, torch.bfloat16), (None, n_heads * (dim + rot_dim)))
+    n = q.shape[0]
+    _need(kvx, "kvx", q.dtype, (n, n_heads * (dim + value_dim)))
+    _need(dkv, "dkv", torch.float32, (n, None), contiguous=False)
+    if dkv.shape[1] < rank + rot_dim or dkv.stride(1) != 1:
+        raise KernelError(f"latent_pack: dkv {tuple(dkv.shape)} holds no {rank} + {rot_dim} values per row")
+    _need(inv_freq, "inv_freq", torch.float32, (rot_dim // 2,))
+    _need(seq_page0, "seq_page0", torch.int32, (None,))
+    q_pad = torch.empty((n, n_heads * key_width), dtype=q.dtype, device=q.device)
+    k_rows = torch.empty((n_pages, n_heads, page_size, key_width), dtype=q.dtype, device=q.device)
+    v_rows = torch.empty((n_pages, n_heads, page_size, value_width), dtype=q.dtype, device=q.device)
+    _check(_fn("latent", "zk_latent_pack")(
+        _ptr(q), _ptr(kvx), kvx.stride(0), _ptr(dkv), dkv.stride(0), _ptr(inv_freq), _ptr(q_pad), _ptr(k_rows), _ptr(v_rows),
+        _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_page0), n, n_heads, dim, rot_dim, value_dim, rank, key_width, value_width,
+        page_size, dtype_code(q.dtype), _stream()), "latent_pack")
+    return q_pad, k_rows, v_rows
 
 
 def head_gemm(a: torch.Tensor, a_head: int, w: torch.Tensor, out: torch.Tensor, o_head: int,
@@ -1147,22 +1179,26 @@ def _takes(lib: str, fn: str, n_heads: int, n_kv: int, head_dim: int, page_size:
 @functools.lru_cache(maxsize=None)      # a pure function of sizes, asked for by every attention layer of every step
 def attention_plan(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, page_size: int,
                    single_token: bool, window: int = 0, value_dim: Optional[int] = None,
-                   biased: bool = False, talking: bool = False, extras: bool = False) -> tuple[str, int]:
+                   biased: bool = False, talking: bool = False, extras: bool = False,
+                   kept_or_sink: bool = False) -> tuple[str, int]:
     """Which attention kernel runs for these sizes and how many tokens its query tiles hold:
     ("single_token_tc" | "single_token" | "prompt_tc5" | "prompt_tc" | "general", tokens per tile).
     Values of another width than the keys go to the general kernel; a distance bias on the scores is
     taken by the general kernel and the two mma.sync kernels ("prompt_tc", "single_token_tc"); weights that
-    are mixed across the heads after the softmax (`talking`) by those three and the tcgen05 prompt kernel."""
+    are mixed across the heads after the softmax (`talking`) by those three and the tcgen05 prompt kernel.
+    `kept_or_sink`: kept first tokens or a sink in the softmax, which the general kernel and the two mma.sync kernels
+    take (without a bias or mixed weights); `extras`: values read from the key rows, the general kernel's."""
     same_width = value_dim is None or value_dim == head_dim
-    if extras:          # kept first tokens, a sink, values read from the key rows: the general kernel's
+    if extras or (kept_or_sink and (biased or talking)):
         return "general", attn_tile_shape(n_heads, n_kv)[0]
     if same_width and dtype == torch.bfloat16 and n_heads % n_kv == 0:
-        if (not single_token and window <= 0 and not biased and _may_take("attention_prefill_tc5", n_heads, n_kv, head_dim, page_size)
+        if (not single_token and window <= 0 and not biased and not kept_or_sink and _may_take("attention_prefill_tc5", n_heads, n_kv, head_dim, page_size)
                 and _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_takes")(n_heads, n_kv, head_dim, page_size, window)):
             return "prompt_tc5", _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_tile_tokens")(n_heads, n_kv)
         if single_token and _takes("attention_decode_tc", "zk_attn_decode_tc_takes", n_heads, n_kv, head_dim, page_size):
             return "single_token_tc", 1
-        if single_token and not biased and not talking and _takes("attention_decode", "zk_attn_decode_takes", n_heads, n_kv, head_dim, page_size):
+        if (single_token and not biased and not talking and not kept_or_sink
+                and _takes("attention_decode", "zk_attn_decode_takes", n_heads, n_kv, head_dim, page_size)):
             return "single_token", 1
         if not single_token and _takes("attention_prefill", "zk_attn_prefill_takes", n_heads, n_kv, head_dim, page_size):
             return "prompt_tc", _fn("attention_prefill", "zk_attn_prefill_tile_tokens")(n_heads, n_kv)
@@ -1178,7 +1214,7 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
     `keep_first`: with a window, the first so many positions of a sequence stay visible to every later query.
     `sink` float32 [H]: exp(sink_h) is one more term of head h's softmax denominator (no key, no value, not scaled).
     `values_in_keys`: there is no value cache; a value row is the first `value_dim` entries of the key row.
-    All three are the general kernel's.  With
+    The last is the general kernel's; the first two also the two mma.sync kernels' ("prompt_tc", "single_token_tc").  With
     num_splits > 1 the keys are cut at multiples of `split_keys` and merged afterwards.
     `single_token` says that every sequence brings exactly one query (row b = sequence b); the
     bfloat16 kernels for that case are used when they take the sizes.  `kind` names the kernel as
@@ -1200,9 +1236,12 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
         v_cache = k_cache
     else:
         _need(v_cache, "v_cache", q.dtype, (None, n_kv, None, vd))
-    extras = keep_first > 0 or sink is not None or values_in_keys
-    if extras and kind not in (None, "general"):
-        raise KernelError(f"attention: the '{kind}' kernel takes no kept first tokens, sink or values in the key rows")
+    kept_or_sink = keep_first > 0 or sink is not None
+    if values_in_keys and kind not in (None, "general"):
+        raise KernelError(f"attention: the '{kind}' kernel takes no values in the key rows")
+    if kept_or_sink and kind not in (None, "general", "prompt_tc", "single_token_tc"):
+        raise KernelError(f"attention: the '{kind}' kernel takes no kept first tokens or sink")
+    extras = values_in_keys or (kept_or_sink and kind in (None, "general"))
     if sink is not None:
         _need(sink, "sink", torch.float32, (n_heads,))
     if bias is not None:
@@ -1254,21 +1293,22 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
         _check(_fn("attention_prefill", "zk_attn_prefill")(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq), _ptr(tile_q0), _ptr(cu_q),
             _ptr(seq_start), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n_tiles, n_heads, n_kv, head_dim,
-            page_size, window, scale, r1, r2, _ptr(part_o) if talk is not None else None,
-            _ptr(part_ml) if talk is not None else None, _stream()), "attention (prompt, tensor cores)")
+            head_dim, page_size, window, scale, r1, r2, _ptr(part_o) if talk is not None else None,
+            _ptr(part_ml) if talk is not None else None, int(keep_first), _ptr(sink), _stream()),
+            "attention (prompt, tensor cores)")
         return out if talk is None else _merge_talk(part_o, part_ml, talk, out, n, n_heads, n_kv, vd, 1)
     if (single_token and kind in (None, "single_token_tc") and q.dtype == torch.bfloat16
             and _takes("attention_decode_tc", "zk_attn_decode_tc_takes", n_heads, n_kv, head_dim, page_size)):
         _check(_fn("attention_decode_tc", "zk_attn_decode_tc")(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(seq_start),
             _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n, n_heads, n_kv, head_dim, page_size, window,
-            scale, num_splits, split_keys, r1, r2, 1 if talk is not None else 0, _stream()),
+            scale, num_splits, split_keys, r1, r2, 1 if talk is not None else 0, int(keep_first), _ptr(sink), _stream()),
             "attention (single token, tensor cores)")
         if talk is not None:
             return _merge_talk(part_o, part_ml, talk, out, n, n_heads, n_kv, vd, num_splits)
         if num_splits > 1:
             _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, head_dim,
-                                                     num_splits, dtype_code(q.dtype), None, n_heads, _stream()), "attention merge")
+                                                     num_splits, dtype_code(q.dtype), _ptr(sink), n_heads, _stream()), "attention merge")
         return out
     if kind == "single_token_tc":
         raise KernelError("attention: the tensor-core single-token kernel does not take these sizes")
@@ -1294,6 +1334,38 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
         _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, vd,
                                                  num_splits, dtype_code(q.dtype), _ptr(sink), n_heads, _stream()),
                "attention merge")
+    return out
+
+
+def attention_step_rows_takes(dtype: torch.dtype, head_dim: int, value_dim: int, page_size: int) -> bool:
+    """Whether `attention_step_rows` runs for these widths."""
+    return (dtype == torch.bfloat16 and (head_dim, value_dim) in ((64, 64), (128, 128), (128, 64))
+            and _may_take("attention_prefill", 1, 1, head_dim, page_size))
+
+
+def attention_step_rows_tile_tokens(n_heads: int) -> int:
+    return _fn("attention_prefill", "zk_attn_prefill_tile_tokens")(n_heads, n_heads)
+
+
+def attention_step_rows(q, k_rows, v_rows, tile_seq, tile_q0, cu_q, seq_start, seq_page0, n_heads: int, scale: float) -> torch.Tensor:
+    """Causal attention of a prompt step over keys and values that the step itself laid out (no cache): every head
+    has keys and values of its own, k_rows [pages, H, page_size, head_dim] and v_rows [pages, H, page_size,
+    value_dim], sequence b's position pos at row pos % page_size of page seq_page0[b] + pos // page_size.
+    q [n, H * head_dim]; returns [n, H * value_dim].  bfloat16 on the tensor-core prompt kernel; the tiles hold
+    `attention_step_rows_tile_tokens` tokens."""
+    _need(k_rows, "k_rows", torch.bfloat16, (None, n_heads, None, None))
+    hd, page_size = k_rows.shape[3], k_rows.shape[2]
+    _need(v_rows, "v_rows", torch.bfloat16, (k_rows.shape[0], n_heads, page_size, None))
+    vd = v_rows.shape[3]
+    _need(q, "q", torch.bfloat16, (None, n_heads * hd))
+    if not attention_step_rows_takes(q.dtype, hd, vd, page_size):
+        raise KernelError(f"attention over a step's own rows: no kernel for keys of {hd} and values of {vd}")
+    n = q.shape[0]
+    out = torch.empty((n, n_heads * vd), dtype=q.dtype, device=q.device)
+    _check(_fn("attention_prefill", "zk_attn_prefill")(
+        _ptr(q), _ptr(k_rows), _ptr(v_rows), _ptr(out), _ptr(tile_seq), _ptr(tile_q0), _ptr(cu_q), _ptr(seq_start),
+        _ptr(seq_page0), None, 0, tile_seq.numel(), n_heads, n_heads, hd, vd, page_size, 0, scale, None, None, None, None,
+        0, None, _stream()), "attention (prompt, a step's own rows)")
     return out
 
 

@@ -237,7 +237,7 @@ class GqaAttention(Mixer):
         kind, tile_tokens = kernels.attention_plan(q.dtype, self.n_heads, self.n_kv, self.head_dim, kv.page_size,
                                                    ctx.is_decode, self.window, self.value_dim,
                                                    self.distance_bias is not None, self.talk_name is not None,
-                                                   self.keep_first > 0 or self.sink is not None)
+                                                   kept_or_sink=self.keep_first > 0 or self.sink is not None)
         tile_seq, tile_q0 = ctx.memo(("query tiles", tile_tokens), lambda: self._tiles_on_device(ctx, tile_tokens))
         num_splits, split_keys = (key_chunks(ctx.n_seqs, self.n_kv, ctx.max_kv_len, self._sm_count, self.split_keys)
                                   if ctx.is_decode else (1, 0))

@@ -16,6 +16,11 @@ first r entries also serve as the values, and expands the result with W_uv,h aft
 a token whatever H is, and nothing is expanded for the tokens of earlier steps.  Norms, angles, scores, softmax and the
 gate are float32; the gate's logits and the latents leave their contraction as float32.
 
+A prompt step that starts its sequences reads nothing cached, and there the other order is cheaper: the step's own
+tokens get every head's k_h and v_h (one contraction of c against [W_uk; W_uv]), a kernel lays [k_h | k_rot] and v_h
+out in rows padded to the widths the tensor-core prompt kernel takes, and ordinary attention over those rows costs
+d + p multiplications a score instead of r + p.  The cache rows are written all the same, for the steps that follow.
+
 The output gate is optional (`gate_name` None = none), as is the query latent (`q_down_name` None: q = W_uq h)."""
 from __future__ import annotations
 
@@ -81,6 +86,19 @@ class LatentAttention(Mixer):
         self.w_uk_t = weights[self.k_up_name].reshape(H, d, r).transpose(1, 2).contiguous()      # [H, r, d]
         self.w_uv = weights[self.v_up_name].reshape(H, e, r).contiguous()                         # [H, e, r]
         self.w_out = weights[self.out_name]
+        # for prompt steps that expand keys and values: [W_uk; W_uv] as one weight, and W_o with zero columns where
+        # the attention kernel's value rows are wider than e
+        self.w_ukv = self.w_out_wide = None
+        self.key_width = self.value_width = 0
+        if dtype == torch.bfloat16 and d + self.rot_dim <= 128 and e <= 128:
+            kw, vw = (64 if d + self.rot_dim <= 64 else 128), (64 if e <= 64 else 128)
+            self.key_width, self.value_width = max(kw, vw), vw
+            self.w_ukv = torch.cat([weights[self.k_up_name], weights[self.v_up_name]], dim=0).contiguous()
+            self.w_out_wide = self.w_out
+            if vw != e:
+                wide = torch.zeros((self.hidden, H, vw), dtype=self.w_out.dtype, device=self.w_out.device)
+                wide[:, :, :e] = self.w_out.reshape(self.hidden, H, e)
+                self.w_out_wide = wide.reshape(self.hidden, H * vw).contiguous()
         self.q_norm = weights[self.q_norm_name] if self.q_norm_name is not None else None
         self.c_norm = weights[self.kv_norm_name]
         i = np.arange(self.rot_dim // 2, dtype=np.float64)
@@ -115,6 +133,9 @@ class LatentAttention(Mixer):
         q = linear(cq, self.w_uq)                                      # [n, H * (d + p)]
         dkv = low[:, :r + p]
         gate = low[:, r + p:r + p + H] if self.gate_name is not None else None
+        if (self.w_ukv is not None and ctx.from_start and not ctx.is_decode and call.writes_kv
+                and kernels.attention_step_rows_takes(q.dtype, self.key_width, self.value_width, kv.page_size)):
+            return self._forward_expanded(ctx, kv, q, dkv, gate, out, accumulate)
         q_full = torch.empty((n, H * (r + p)), dtype=q.dtype, device=q.device)
         kernels.latent_prepare(q, q_full, dkv, self.c_norm, self.inv_freq, kv.k, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot,
                                kv.page_table, H, d, p, r, self.eps, ctx.status, write_kv=call.writes_kv)
@@ -130,6 +151,28 @@ class LatentAttention(Mixer):
         att = torch.empty((n, H * e), dtype=q.dtype, device=q.device)
         self._per_head(lat, r, self.w_uv, att, e, gate)
         linear(att, self.w_out, out=out, accumulate=accumulate)
+
+
+    def _forward_expanded(self, ctx, kv, q, dkv, gate, out, accumulate):
+        """A prompt step whose sequences start at position 0: keys and values expanded for the step's own tokens."""
+        H, d, p, e, r = self.n_heads, self.dim, self.rot_dim, self.value_dim, self.kv_rank
+        n, page = ctx.n_tokens, kv.page_size
+        c = torch.empty((n, r), dtype=q.dtype, device=q.device)
+        kernels.latent_prepare(q, None, dkv, self.c_norm, self.inv_freq, kv.k, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot,
+                               kv.page_table, H, d, p, r, self.eps, ctx.status, write_kv=True, c_out=c)
+        kvx = linear(c, self.w_ukv)                                    # [n, H * d + H * e]
+        pages = [-(-l // page) for l in ctx.q_lens]
+        first = ctx.memo(("step pages", page), lambda: torch.from_numpy(
+            (np.cumsum([0] + pages[:-1])).astype(np.int32)).to(ctx.device, non_blocking=True))
+        q_pad, k_rows, v_rows = kernels.latent_pack(q, kvx, dkv, self.inv_freq, ctx.tok_seq, ctx.tok_pos, first, sum(pages), page,
+                                                    H, d, p, e, r, self.key_width, self.value_width)
+        tile_tokens = kernels.attention_step_rows_tile_tokens(H)
+        from .attention import GqaAttention
+        tile_seq, tile_q0 = ctx.memo(("query tiles", tile_tokens), lambda: GqaAttention._tiles_on_device(ctx, tile_tokens))
+        att = kernels.attention_step_rows(q_pad, k_rows, v_rows, tile_seq, tile_q0, ctx.cu_q, ctx.seq_start, first, H, self.scale)
+        if gate is not None:
+            kernels.head_gate(att, gate, H)
+        linear(att, self.w_out_wide, out=out, accumulate=accumulate)
 
 
 MIXERS.register("latent_attention", LatentAttention)
