@@ -317,6 +317,8 @@ def plain_latent(x, t, H, d, p, e, r, s, scale, base, eps=2e-6):
     (128, 2, 64, 32, 64, 160, 64, 0.1, 10000.0, 64),          # keys of 96 entries in rows of 128, values of 64
     (128, 2, 96, 32, 128, 160, 64, 0.09, 10000.0, 128),       # keys and values of 128
     (128, 3, 32, 16, 96, 80, 64, 0.14, 500.0, 64),            # values wider than the keys
+    (128, 20, 16, 32, 16, 512, 48, 0.1, 10000.0, 64),         # rows of 544 values, heads in two groups of sixteen
+    (64, 17, 16, 16, 32, 272, 32, 0.15, 100.0, 64),           # rows of 288 values, one head beyond the first group
 ])
 def test_latent_attention_alone(k, dtype, D, H, d, p, e, r, s, scale, base, page):
     t = latent_tensors(D, H, d, p, e, r, s, dtype, 70)

@@ -100,6 +100,10 @@ _SIGNATURES = {
         "zk_attn_prefill_tc5_takes": "iiiii",
         "zk_attn_prefill_tc5_tile_tokens": "ii",
     },
+    "attention_decode_latent": {
+        "zk_attn_decode_latent": "ppppppppiiiiiifiip",
+        "zk_attn_decode_latent_takes": "iiii",
+    },
     "attention_decode_tc": {
         "zk_attn_decode_tc": "pppppppppiiiiiiifii" + "pp" + "i" + "ip" + "p",
         "zk_attn_decode_tc_takes": "iiii",
@@ -1366,6 +1370,42 @@ def attention_step_rows(q, k_rows, v_rows, tile_seq, tile_q0, cu_q, seq_start, s
         _ptr(q), _ptr(k_rows), _ptr(v_rows), _ptr(out), _ptr(tile_seq), _ptr(tile_q0), _ptr(cu_q), _ptr(seq_start),
         _ptr(seq_page0), None, 0, tile_seq.numel(), n_heads, n_heads, hd, vd, page_size, 0, scale, None, None, None, None,
         0, None, _stream()), "attention (prompt, a step's own rows)")
+    return out
+
+
+def attention_latent_single_takes(dtype: torch.dtype, n_heads: int, row_dim: int, value_dim: int, page_size: int) -> bool:
+    """Whether `attention_latent_single` runs for these sizes (known here, so that a model it cannot serve never has
+    the library compiled)."""
+    if (dtype != torch.bfloat16 or row_dim % 16 or value_dim % 16 or value_dim > min(row_dim, 512) or row_dim > 768
+            or page_size % 64):
+        return False
+    return bool(_fn("attention_decode_latent", "zk_attn_decode_latent_takes")(n_heads, row_dim, value_dim, page_size))
+
+
+def attention_latent_single(q, cache, seq_start, seq_slot, page_table, n_heads: int, value_dim: int, scale: float,
+                            num_splits: int = 1, split_keys: int = 0) -> torch.Tensor:
+    """Single-token steps of attention over one cached row per token that is key and value at once: q [n, H * W]
+    (sequence b's queries in row b), cache [pages, 1, page_size, W], a value = a row's first `value_dim` entries.
+    Returns [n, H * value_dim].  bfloat16, on the tensor cores; with num_splits > 1 the keys are cut at multiples of
+    `split_keys` and merged afterwards."""
+    _need(cache, "cache", torch.bfloat16, (None, 1, None, None))
+    page_size, W = cache.shape[2], cache.shape[3]
+    _need(q, "q", torch.bfloat16, (None, n_heads * W))
+    n = q.shape[0]
+    if not attention_latent_single_takes(q.dtype, n_heads, W, value_dim, page_size):
+        raise KernelError(f"attention over latent rows: no kernel for rows of {W} with values of {value_dim}")
+    out = torch.empty((n, n_heads * value_dim), dtype=q.dtype, device=q.device)
+    part_o = part_ml = None
+    if num_splits > 1:
+        part_o = torch.empty((num_splits, n * n_heads, value_dim), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((num_splits, n * n_heads, 2), dtype=torch.float32, device=q.device)
+    _check(_fn("attention_decode_latent", "zk_attn_decode_latent")(
+        _ptr(q), _ptr(cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(seq_start), _ptr(seq_slot), _ptr(page_table),
+        page_table.stride(0), n, n_heads, W, value_dim, page_size, scale, num_splits, split_keys, _stream()),
+        "attention (single token, latent rows)")
+    if num_splits > 1:
+        _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, value_dim, num_splits,
+                                                 dtype_code(q.dtype), None, n_heads, _stream()), "attention merge")
     return out
 
 

@@ -140,6 +140,14 @@ class LatentAttention(Mixer):
         kernels.latent_prepare(q, q_full, dkv, self.c_norm, self.inv_freq, kv.k, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot,
                                kv.page_table, H, d, p, r, self.eps, ctx.status, write_kv=call.writes_kv)
         self._per_head(q, d + p, self.w_uk_t, q_full, r + p)           # the unrotated parts, carried to the latent's space
+        if ctx.is_decode and kernels.attention_latent_single_takes(q.dtype, H, r + p, r, kv.page_size):
+            num_splits, split_keys = key_chunks(ctx.n_seqs, 1, ctx.max_kv_len, self._sm_count, self.split_keys)
+            lat = kernels.attention_latent_single(q_full, kv.k, ctx.seq_start, ctx.seq_slot, kv.page_table, H, r, self.scale,
+                                                  num_splits, split_keys)
+            att = torch.empty((n, H * e), dtype=q.dtype, device=q.device)
+            self._per_head(lat, r, self.w_uv, att, e, gate)
+            linear(att, self.w_out, out=out, accumulate=accumulate)
+            return
         kind, tile_tokens = kernels.attention_plan(q.dtype, H, 1, r + p, kv.page_size, ctx.is_decode, 0, r, False, False, True)
         from .attention import GqaAttention
         tile_seq, tile_q0 = ctx.memo(("query tiles", tile_tokens), lambda: GqaAttention._tiles_on_device(ctx, tile_tokens))
