@@ -104,7 +104,8 @@ def test_router_and_routed_experts_both_ways(k, dtype, D, F, E, top, rows):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("D,F,rows,limit", [(48, 56, 5, 2.0), (128, 256, 40, 1.0), (38, 50, 130, 0.75), (256, 320, 1, 1.5)])
+@pytest.mark.parametrize("D,F,rows,limit", [(48, 56, 5, 2.0), (128, 256, 40, 1.0), (38, 50, 130, 0.75), (256, 320, 1, 1.5),
+                                            (128, 256, 300, 1.0), (64, 48, 200, 0.5), (128, 384, 20, 0.8)])
 def test_clamped_glu_part(k, dtype, D, F, rows, limit):
     from zinfer_b200.parts import ClampedGLU
     t = {"gate": rnd((F, D), 1, dtype, 2 * D ** -0.5), "up": rnd((F, D), 2, dtype, 2 * D ** -0.5), "down": rnd((D, F), 3, dtype, F ** -0.5)}

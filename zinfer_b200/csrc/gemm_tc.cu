@@ -41,6 +41,16 @@ constexpr int BK = 64;           // k block: 64 bfloat16 = one 128-byte swizzle 
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;     // producer warp, MMA warp, four epilogue warps
 
+// The gated unit of the fused epilogues: silu(g) * u, or with limit > 0 the clamped unit described in Params.
+__device__ __forceinline__ float glu_unit(float g, float u, float limit, float alpha) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit) + 1.0f;
+    return g / (1.0f + expf(-alpha * g)) * u;
+  }
+  return g / (1.0f + expf(-g)) * u;
+}
+
 struct Params {
   void* C;
   const float* bias;
@@ -48,6 +58,9 @@ struct Params {
   int M, N, K;         // M tokens, N weight rows
   int ldc, accumulate, splits;
   int swiglu;          // normal mode: W rows are groups of 16 gate rows + their 16 up rows; C [M, N/2] = silu(g)*u
+  // with swiglu and glu_limit > 0 the unit is the clamped one: g = min(g, limit), u = clamp(u, -limit, limit),
+  // C = g * sigmoid(glu_alpha * g) * (u + 1)
+  float glu_limit, glu_alpha;
   // Up to 64 tokens only.  ssq_in: X holds bfloat16(x * norm weight) of rows whose RMSNorm is still to be
   // applied, ssq_in [M, ssq_parts] partial sums of x^2: token t's sums are scaled by
   // 1 / sqrt(sum(ssq_in[t]) / K + eps).  emit_x: beside C (the float32 residual rows) the kernel writes
@@ -288,7 +301,7 @@ __global__ void __launch_bounds__(THREADS)
             const int gc = (oc / 16) * 32 + (oc % 16);      // its gate's column; the up is 16 further
             if (h_base + oc < F) {
               const float gate = srow[gc], up = srow[gc + 16];
-              hrow[oc] = from_f32<TC>(gate / (1.0f + expf(-gate)) * up);
+              hrow[oc] = from_f32<TC>(glu_unit(gate, up, p.glu_limit, p.glu_alpha));
             }
           }
         }
@@ -369,7 +382,7 @@ __global__ void __launch_bounds__(THREADS)
           for (int j = 0; j < 16; ++j) {
             const float up = __shfl_down_sync(0xffffffffu, v[j], 16);
             if ((lane & 16) == 0 && n < p.N && c0 + j < p.M)
-              C[(size_t)(c0 + j) * p.ldc + f] = from_f32<TC>(v[j] / (1.0f + expf(-v[j])) * up);
+              C[(size_t)(c0 + j) * p.ldc + f] = from_f32<TC>(glu_unit(v[j], up, p.glu_limit, p.glu_alpha));
           }
         } else {
           const bool n_in = n < p.N;
@@ -446,7 +459,7 @@ __global__ void __launch_bounds__(THREADS)
                 // as in the unsplit epilogue: a warp's rows are 16 gate rows and their 16 up rows
                 const float up = __shfl_down_sync(0xffffffffu, acc, 16);
                 if ((lane & 16) == 0 && n_in)
-                  C[(size_t)t * p.ldc + (n >> 5) * 16 + (n & 15)] = from_f32<TC>(acc / (1.0f + expf(-acc)) * up);
+                  C[(size_t)t * p.ldc + (n >> 5) * 16 + (n & 15)] = from_f32<TC>(glu_unit(acc, up, p.glu_limit, p.glu_alpha));
               } else if (n_in) {
                 acc += old[i];
                 C[(size_t)t * p.ldc + n] = from_f32<TC>(acc);
@@ -714,7 +727,7 @@ __global__ void __launch_bounds__(THREADS, PAIR ? 1 : 0)
         if (p.swiglu) {    // columns: 16 gates, then their 16 ups
           float o[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) o[j] = v[j] / (1.0f + expf(-v[j])) * v[j + 16];
+          for (int j = 0; j < 16; ++j) o[j] = glu_unit(v[j], v[j + 16], p.glu_limit, p.glu_alpha);
           stage_row<TC, 16>(row, lane, part * (16 * (int)sizeof(TC) / 16), o);
         } else {
           if (p.bias) {
@@ -901,14 +914,15 @@ int zk_gemm_tc_fuses_epilogue(int M, int N, int ldc, int out_dtype, int accumula
 // M <= 64 runs swapped (weights on the 128-row side) with K cut into `splits` parts (rounded down
 // to 1, 2, 4 or 8: a cluster's size); larger M runs normal and ignores splits.  With `swiglu`
 // W's rows are groups of 16 gate rows and their 16 up rows and C [M, N/2] receives
-// silu(gate) * up (src/model.zig:1085-1117).  M <= 64 only: ssq_in [M, ssq_parts] (or null) says
+// silu(gate) * up (src/model.zig:1085-1117), or with glu_limit > 0 the clamped unit min(g, limit) *
+// sigmoid(glu_alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1).  M <= 64 only: ssq_in [M, ssq_parts] (or null) says
 // that X is bfloat16(x * norm weight) and scales token t's sums by 1 / sqrt(sum(ssq_in[t]) / K +
 // eps); emit_x (or null; float32 C, no SwiGLU) is written as bfloat16(C * emit_w), [M, N], and
 // emit_ssq [M, ceil(N / 32)] as the sums of C^2 over 32 columns.
 int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, int N, int K, int ldx, int ldw, int ldc,
                int out_dtype, int accumulate, int splits, int swiglu, const float* ssq_in, int ssq_parts, float eps,
                const float* emit_w, void* emit_x, float* emit_ssq, int* status, const float* col_scale, int act,
-               cudaStream_t stream) {
+               float glu_limit, float glu_alpha, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if ((ssq_in || emit_x) && M > 64) return ZK_EINVAL;
   if ((col_scale || act) && (act < 0 || act > 1 || swiglu || !zk_gemm_tc_fuses_epilogue(M, N, ldc, out_dtype, accumulate)))
@@ -925,6 +939,7 @@ int zk_gemm_tc(const void* X, const void* W, void* C, const float* bias, int M, 
   p.ssq_in = ssq_in; p.ssq_parts = ssq_parts; p.eps = eps;
   p.emit_w = emit_w; p.emit_x = (bf16*)emit_x; p.emit_ssq = emit_ssq;
   p.col_scale = col_scale; p.act = act;
+  p.glu_limit = swiglu ? glu_limit : 0.f; p.glu_alpha = glu_alpha;
   CUtensorMap ma, mb, mc;
   const bool f32 = out_dtype == ZK_F32;
   if (M > 64) {

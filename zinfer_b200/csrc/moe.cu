@@ -195,6 +195,46 @@ __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict
   for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = t < 0 ? from_f32<T>(0.f) : src[d];
 }
 
+// The rows of a prompt step sorted by expert, made where the router left its choice (no trip to the host):
+// ids [P] names the expert of pair i = t * top + k.  Expert e's pairs get the rows start_e .. start_e + count_e - 1,
+// start_e a multiple of `tile` (every expert's rows are padded to whole tiles); row_token [cap] = the token of each
+// row, -1 for a padding row; pair_row [P] = the row of each pair; tile_group [cap / tile] = the expert of each tile
+// (0 for the tiles behind the last expert's, whose rows are all padding).  cap >= P rounded down to tiles plus one
+// tile per expert.  One block; the order of an expert's rows is not fixed, which no row's result depends on.
+__global__ void __launch_bounds__(1024)
+    moe_expert_rows_kernel(const int* __restrict__ ids, int P, int E, int top, int tile, int cap,
+                           int* __restrict__ row_token, int* __restrict__ pair_row, int* __restrict__ tile_group) {
+  extern __shared__ int sh[];      // count [E], start [E]
+  int* count = sh;
+  int* start = sh + E;
+  zk_let_next_start();
+  zk_wait_prior();
+  const int tid = threadIdx.x, nt = blockDim.x;
+  for (int e = tid; e < E; e += nt) count[e] = 0;
+  for (int i = tid; i < cap; i += nt) row_token[i] = -1;
+  __syncthreads();
+  for (int i = tid; i < P; i += nt) atomicAdd(&count[min(max(ids[i], 0), E - 1)], 1);
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) {
+      start[e] = run;
+      const int tiles = (count[e] + tile - 1) / tile;
+      for (int t = 0; t < tiles; ++t) tile_group[run / tile + t] = e;
+      run += tiles * tile;
+      count[e] = 0;            // from here on the expert's next free row
+    }
+    for (int t = run / tile; t < cap / tile; ++t) tile_group[t] = 0;
+  }
+  __syncthreads();
+  for (int i = tid; i < P; i += nt) {
+    const int e = min(max(ids[i], 0), E - 1);
+    const int r = start[e] + atomicAdd(&count[e], 1);
+    row_token[r] = i / top;
+    pair_row[i] = r;
+  }
+}
+
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_row, float* __restrict__ out,
                                    int D, int top, int accumulate, const float* __restrict__ route_w) {
   zk_let_next_start();
@@ -380,6 +420,15 @@ int zk_moe_router(const void* x, const float* w_router, int* route_ids, float* r
   if (dtype == ZK_BF16) ZK_ROUTER(bf16);
 #undef ZK_ROUTER
   return ZK_EINVAL;
+}
+
+// The device's own sort of (token, k) pairs by expert, as moe_expert_rows_kernel describes it.
+int zk_moe_expert_rows(const int* ids, int P, int E, int top, int tile, int cap, int* row_token, int* pair_row,
+                       int* tile_group, cudaStream_t stream) {
+  if (P <= 0) return 0;
+  if (E <= 0 || E > 4096 || top <= 0 || tile <= 0 || cap % tile || cap < (P / tile + E) * tile) return ZK_EINVAL;
+  return zk_launch_dependent(moe_expert_rows_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * (size_t)E, stream, ids, P, E,
+                             top, tile, cap, row_token, pair_row, tile_group);
 }
 
 // xg[r, :] = x[row_token[r], :] for r < n_rows, zeros where row_token[r] < 0 (rows in the run dtype, D elements).

@@ -60,6 +60,7 @@ _SIGNATURES = {
         "zk_moe_combine": "pppiiii" + "p" + "p",
         "zk_moe_routed": "ppppippp" + "iiiiiii" + "pp",
         "zk_moe_router": "pppp" + "iiiii" + "p",
+        "zk_moe_expert_rows": "piiiiipppp",
     },
     "gemm_simt": {
         "zk_gemm_simt": "ppppiiiiiiiiip",
@@ -72,7 +73,7 @@ _SIGNATURES = {
         "zk_gemm_skinny_fused_max_m": "",
     },
     "gemm_tc": {
-        "zk_gemm_tc": "ppppiiiiiiiiii" + "pifppp" + "p" + "pi" + "p",
+        "zk_gemm_tc": "ppppiiiiiiiiii" + "pifppp" + "p" + "pi" + "ff" + "p",
         "zk_gemm_tc_fuses_epilogue": "iiiii",
         "zk_gemm_tc_force_form": "i",
         "zk_gemm_tc_grouped": "pppiiiiiiiippp",
@@ -582,8 +583,10 @@ def gemm_tc_emits(a, out: Optional[torch.Tensor]) -> bool:
 def gemm_tc(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=None,
             accumulate: bool = False, bias: Optional[torch.Tensor] = None, splits: int = 1,
             swiglu: bool = False, emit: Optional["NormEmit"] = None, col_scale: Optional[torch.Tensor] = None,
-            act: Optional[str] = None) -> torch.Tensor:
+            act: Optional[str] = None, glu_clamp: Optional[tuple] = None) -> torch.Tensor:
     """out (+)= a @ w.T (+ bias) with TMA-fed tcgen05 MMAs and the accumulator in tensor memory.
+    `glu_clamp` = (limit, alpha), with `swiglu`: the unit is min(g, limit) * sigmoid(alpha * min(g, limit)) *
+    (clamp(u, -limit, limit) + 1) in place of silu(g) * u.
     `act` ("relu_squared") and `col_scale` (float32 [N]) as in `gemm_skinny`, where `gemm_tc_fuses` says so.
     More than 64 rows: persistent blocks on 256-wide tiles when N is a multiple of 256 (pairs of
     blocks with tcgen05.mma.cta_group::2 above 128 rows, TMA stores), else one 128 x 128 tile of
@@ -603,6 +606,8 @@ def gemm_tc(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=No
     N = w.shape[0]
     if swiglu and (N % 32 or accumulate or bias is not None):
         raise KernelError("gemm_tc: the SwiGLU epilogue needs N a multiple of 32, no bias and no accumulation")
+    if glu_clamp is not None and (not swiglu or not glu_clamp[0] > 0):
+        raise KernelError("gemm_tc: the clamped unit goes with the gated epilogue and a positive limit")
     n_out = N // 2 if swiglu else N
     if out is None:
         if accumulate:
@@ -629,7 +634,8 @@ def gemm_tc(a, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=No
                                         1 if swiglu else 0, ssq, ssq_parts, eps,
                                         _ptr(emit.weight) if emit else None, _ptr(emit.xw) if emit else None,
                                         _ptr(emit.ssq) if emit else None, _ptr(status_word(a.device)), _ptr(col_scale),
-                                        1 if act else 0, _stream()),
+                                        1 if act else 0, float(glu_clamp[0]) if glu_clamp else 0.0,
+                                        float(glu_clamp[1]) if glu_clamp else 0.0, _stream()),
            "gemm_tc")
     return out
 
@@ -957,6 +963,21 @@ def moe_router(x: torch.Tensor, w_router: torch.Tensor, top: int) -> tuple[torch
     _check(_fn("moe", "zk_moe_router")(_ptr(x), _ptr(w_router), _ptr(ids), _ptr(wts), n, D, E, top, dtype_code(x.dtype),
                                        _stream()), "moe_router")
     return ids, wts
+
+
+def moe_expert_rows(route_ids: torch.Tensor, n_experts: int, tile: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """The (token, k) pairs of route_ids [n, top] (int32, device) sorted by expert on the device, every expert's rows
+    padded to whole tiles: (row_token [cap] with -1 for padding rows, pair_row [n * top], tile_group [cap / tile]),
+    cap = the most rows any choice can need.  Tiles behind the last expert's hold padding rows only."""
+    _need(route_ids, "route_ids", torch.int32, (None, None))
+    n, top = route_ids.shape
+    P = n * top
+    cap = (P // tile + n_experts) * tile
+    words = torch.empty(cap + P + cap // tile, dtype=torch.int32, device=route_ids.device)
+    row_token, pair_row, tile_group = words[:cap], words[cap:cap + P], words[cap + P:]
+    _check(_fn("moe", "zk_moe_expert_rows")(_ptr(route_ids), P, n_experts, top, tile, cap, _ptr(row_token), _ptr(pair_row),
+                                            _ptr(tile_group), _stream()), "moe_expert_rows")
+    return row_token, pair_row, tile_group
 
 
 def moe_routed(x: torch.Tensor, route_ids: torch.Tensor, route_w: torch.Tensor, w_gate_up: torch.Tensor, interleave: int,

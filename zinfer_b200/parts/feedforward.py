@@ -20,6 +20,7 @@ class SwiGLU(FeedForward):
         self.hidden, self.ffn_dim = hidden, ffn_dim
         self.gate_name, self.up_name, self.down_name = gate_name, up_name, down_name
         self.w_gate_up = self.w_down = None
+        self.clamp = None        # (limit, alpha) of a unit with clamps, which the contraction's epilogue also takes
         # With F a multiple of 16 the stacked matrix is stored as groups of 16 gate rows followed by
         # their 16 up rows, which lets a contraction kernel apply the activation in its epilogue.
         self.interleave = FUSION_GROUP if ffn_dim % FUSION_GROUP == 0 else 0
@@ -40,7 +41,7 @@ class SwiGLU(FeedForward):
             from . import linear_bf16
             rows_in = xn.shape[0]
             tc_rows = linear_bf16.TC_SWAPPED_MIN_ROWS <= rows_in <= kernels.gemm_skinny_max_m()
-            x = None if tc_rows else fused_input(xn, w, need_fused_rows=True, blocks=self.ffn_dim // 16)
+            x = None if tc_rows or self.clamp else fused_input(xn, w, need_fused_rows=True, blocks=self.ffn_dim // 16)
             if x is not None:                       # few rows: gate, up and the activation in one kernel
                 h = kernels.gemm_skinny_swiglu(x, w)
             else:
@@ -51,10 +52,14 @@ class SwiGLU(FeedForward):
                 # prompt steps, and steps of 17..64 rows: activation in the epilogue
                 if (rows > kernels.gemm_skinny_max_m() or tc_rows) and kernels.gemm_tc_takes(x, w):
                     splits = swapped_splits(w.shape[0], kernels.sm_count(w.device)) if tc_rows else 1
-                    h = kernels.gemm_tc(x, w, swiglu=True, splits=splits)
+                    h = kernels.gemm_tc(x, w, swiglu=True, splits=splits, glu_clamp=self.clamp)
         if h is None:
-            h = kernels.silu_mul(linear(xn, w), self.interleave)
+            h = self.unit(linear(xn, w))
         linear(h, self.w_down, out=out, accumulate=accumulate)
+
+    def unit(self, gu):
+        """The gated unit of [gate | up] rows as the stacked weight leaves them, where no contraction applied it."""
+        return kernels.silu_mul(gu, self.interleave)
 
 
 class ClampedGLU(SwiGLU):
@@ -63,7 +68,8 @@ class ClampedGLU(SwiGLU):
         g = min(xn W_gate^T, limit),  u = clamp(xn W_up^T, -limit, limit),  h = g * sigmoid(alpha * g) * (u + 1),
         out (+)= h W_down^T
 
-    `limit` and `alpha` are constructor parameters; the unit is evaluated in float32.  Weights are stacked as in `SwiGLU`."""
+    `limit` and `alpha` are constructor parameters; the unit is evaluated in float32.  Weights are stacked as in `SwiGLU`,
+    and the contraction kernels that apply silu(g) * u in their epilogue apply this unit there too."""
 
     def __init__(self, hidden: int, ffn_dim: int, gate_name: str, up_name: str, down_name: str, limit: float,
                  alpha: float = 1.702):
@@ -71,10 +77,10 @@ class ClampedGLU(SwiGLU):
         if not limit > 0:
             raise ValueError(f"clamped GLU: the limit must be positive, got {limit}")
         self.limit, self.alpha = float(limit), float(alpha)
+        self.clamp = (self.limit, self.alpha)
 
-    def forward(self, ctx, xn, out, accumulate):
-        h = kernels.clamped_glu(linear(xn, self.w_gate_up), self.limit, self.alpha, self.interleave)
-        linear(h, self.w_down, out=out, accumulate=accumulate)
+    def unit(self, gu):
+        return kernels.clamped_glu(gu, self.limit, self.alpha, self.interleave)
 
 
 class ActMlp(FeedForward):

@@ -197,8 +197,9 @@ class RoutedMoE(TableMoE):
 
     The router runs on the device (`kernels.moe_router`: ids and weights per token).  Few tokens: the two
     weight-streaming kernels read them there, so a single-token step needs nothing from the host and can be
-    recorded.  Many tokens (prompt steps): the chosen ids come to the host once per call, the rows are sorted by
-    expert there and the grouped tensor-core contractions of `TableMoE` run them."""
+    recorded.  Many tokens (prompt steps): a kernel sorts the rows by expert, every expert's rows padded to whole
+    tiles, and the grouped tensor-core contractions of `TableMoE` run them; where those do not take the sizes, the
+    chosen ids come to the host once per call and the experts run one after the other."""
 
     takes_residual_rows = False
     takes_pending_norm = True
@@ -234,6 +235,16 @@ class RoutedMoE(TableMoE):
         if ctx.is_decode or rows.shape[0] < GROUPED_MIN_TOKENS:
             kernels.moe_routed(rows, ids, wts, self.w_gate_up, self.interleave, self.w_down, ctx.status, out=out,
                                accumulate=accumulate)
+            return
+        tile = kernels.GEMM_TC_GROUP_ROWS
+        if (self.interleave and rows.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.ffn_dim % 8 == 0
+                and rows.is_contiguous() and self.n_experts <= 4096):
+            # the rows are sorted by expert where the router left its choice: the step never waits for the host
+            row_token, pair_row, tile_group = kernels.moe_expert_rows(ids, self.n_experts, tile)
+            xg = kernels.moe_gather(rows, row_token)
+            h = kernels.gemm_tc_grouped(xg, self.w_gate_up, tile_group, swiglu=True)
+            y = kernels.gemm_tc_grouped(h, self.w_down, tile_group, out_dtype=torch.float32)
+            kernels.moe_combine(y, pair_row, self.top, out, accumulate, wts)
             return
         chosen = ids.cpu().numpy().reshape(-1).astype(np.int64)
         self._expert_by_expert(ctx, rows, None, out, accumulate, chosen=np.clip(chosen, 0, self.n_experts - 1), weights=wts)
