@@ -135,18 +135,19 @@ __global__ void __launch_bounds__(DL_THREADS)
     const int kb = c0 + t * DL_TK + 8 * warp;           // this warp's 8 keys of the tile
 
     // S = Q K^T for 16 heads x 8 keys; one ldmatrix of K serves two k steps
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    // (even and odd k steps add into sums of their own, so that one MMA need not wait for the one before it)
+    float s[4] = {0.f, 0.f, 0.f, 0.f}, s_odd[4] = {0.f, 0.f, 0.f, 0.f};
     for (int ks = 0; ks < KS; ks += 2) {
-      unsigned a[4], bfr[4];
+      unsigned a[4], a2[4], bfr[4];
       const int chb = 2 * ks + (lane >> 3);
       ldmatrix_x4(bfr, Ks + (8 * warp + (lane & 7)) * RS + (chb < CHW ? chb : 0) * 8);
       ldmatrix_x4(a, Qs + (lane & 15) * RS + (2 * ks + (lane >> 4)) * 8);
+      if (ks + 1 < KS) ldmatrix_x4(a2, Qs + (lane & 15) * RS + (2 * ks + 2 + (lane >> 4)) * 8);
       mma16816(s, a, bfr[0], bfr[1]);
-      if (ks + 1 < KS) {
-        ldmatrix_x4(a, Qs + (lane & 15) * RS + (2 * ks + 2 + (lane >> 4)) * 8);
-        mma16816(s, a, bfr[2], bfr[3]);
-      }
+      if (ks + 1 < KS) mma16816(s_odd, a2, bfr[2], bfr[3]);
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[i] += s_odd[i];
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {

@@ -268,7 +268,19 @@ __global__ void __launch_bounds__(MOE_WARPS * 32)
   for (int e = warp; e < E; e += MOE_WARPS) {
     const float* wr = w + (size_t)e * D;
     float acc = 0.f;
-    for (int d = lane; d < D; d += 32) acc = fmaf(wr[d], xs[d], acc);
+    if ((D & 3) == 0) {          // rows in pieces of four: a quarter of the loads (D is the model's: one order per model)
+      const float4* w4 = reinterpret_cast<const float4*>(wr);
+      const float4* x4 = reinterpret_cast<const float4*>(xs);
+      for (int d = lane; d < (D >> 2); d += 32) {
+        const float4 a = w4[d], v = x4[d];
+        acc = fmaf(a.x, v.x, acc);
+        acc = fmaf(a.y, v.y, acc);
+        acc = fmaf(a.z, v.z, acc);
+        acc = fmaf(a.w, v.w, acc);
+      }
+    } else {
+      for (int d = lane; d < D; d += 32) acc = fmaf(wr[d], xs[d], acc);
+    }
     acc = warp_sum(acc);
     if (lane == 0) z[e] = acc;
   }
