@@ -333,3 +333,35 @@ def test_latent_attention_alone(k, dtype, D, H, d, p, e, r, s, scale, base, page
         if scale > 1 and dtype == torch.bfloat16:
             continue            # sharp scores amplify the rounding of the scores themselves; the 32-bit run decides
         close(outs[b], ref, dtype, f"sequence {b}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("D,H,d,p,e,r,s,page", [(128, 4, 32, 32, 64, 64, 64, 64), (128, 2, 64, 32, 64, 160, 64, 64),
+                                                (64, 3, 16, 8, 20, 48, 40, 16)])
+def test_latent_attention_in_portions_of_a_prompt(k, dtype, D, H, d, p, e, r, s, page):
+    """Two sequences whose prompts come in portions of unequal sizes (a long later portion, which expands the cached
+    latents once more; a short one behind a long prefix; portions of two tokens; a portion that ends on a page border)."""
+    t = latent_tensors(D, H, d, p, e, r, s, dtype, 170)
+    mixer = make_latent(D, H, d, p, e, r, s, 0.12, 10000.0, t, dtype)
+    xs = [rnd((192, D), 171, dtype), rnd((150, D), 172, dtype)]
+    portions = [[70, 58, 2, 60, 2], [20, 100, 3, 2, 25]]
+    bench = Bench(k, mixer, dtype, n_slots=3, max_seq=256, page=page)
+    held = bench.cache.alloc_slots(3)
+    slots = held[1:]
+    outs = [torch.zeros(x.shape[0], D) for x in xs]
+    done = [0, 0]
+    for step in range(5):
+        lens = [portions[b][step] for b in range(2)]
+        ctx = bench.step(slots, lens)
+        xn = torch.cat([xs[b][done[b]:done[b] + lens[b]] for b in range(2)]).to(dtype).cuda()
+        out = torch.full((xn.shape[0], D), 7.0, device="cuda")
+        mixer.forward(ctx, bench.call, xn, out, False)
+        bench.done(slots, lens)
+        o = 0
+        for b in range(2):
+            outs[b][done[b]:done[b] + lens[b]] = out[o:o + lens[b]].cpu()
+            o += lens[b]
+            done[b] += lens[b]
+    bench.cache.free_slots(held)
+    for b, x in enumerate(xs):
+        close(outs[b], plain_latent(x, t, H, d, p, e, r, s, 0.12, 10000.0), dtype, f"sequence {b}")

@@ -79,7 +79,7 @@ class Bench:
         self.cache.sync()
         buf = torch.from_numpy(pack_batch(slots, starts, [[0] * n for n in lens])).to(self.dev)
         ctx = StepContext(self.dtype, self.dev, self.status, buf, sum(lens), len(slots), lens,
-                          max(s + n for s, n in zip(starts, lens)), from_start=all(s == 0 for s in starts))
+                          max(s + n for s, n in zip(starts, lens)), starts=starts)
         return ctx
 
     def done(self, slots, rows_per_seq):

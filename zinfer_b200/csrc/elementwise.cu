@@ -143,6 +143,25 @@ __global__ void head_gate_kernel(T* __restrict__ rows, const float* __restrict__
   }
 }
 
+// The same for bfloat16 rows whose heads are whole 16-byte pieces: a thread takes one piece (eight values, one gate).
+__global__ void head_gate_vec8_kernel(uint4* __restrict__ rows, const float* __restrict__ gate, int ld_gate, int pieces, int H,
+                                      int per_head) {
+  zk_let_next_start();
+  zk_wait_prior();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= pieces) return;
+  const int th = i / per_head, t = th / H, hh = th - t * H;
+  const float s = 1.0f + expf(-gate[(size_t)t * ld_gate + hh]);
+  uint4 v = rows[i];
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(p[j]);
+    p[j] = __floats2bfloat162_rn(f.x / s, f.y / s);
+  }
+  rows[i] = v;
+}
+
 // out[i] = mean + std * n_i with n_i standard normal, a function of (seed, i) only: two hashed
 // uniforms through Box-Muller.  Fills large random models on the device in milliseconds.
 __device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
@@ -732,6 +751,11 @@ int zk_clamped_glu(const void* gu, void* h, int n, int F, int il, float limit, f
 int zk_head_gate(void* rows, const float* gate, int ld_gate, int n, int H, int width, int dtype, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (H <= 0 || width <= 0 || ld_gate < H) return ZK_EINVAL;
+  if (dtype == ZK_BF16 && width % 8 == 0 && (uintptr_t)rows % 16 == 0 && (size_t)n * H * (width / 8) < 0x7fffffffULL) {
+    const int pieces = n * H * (width / 8);
+    return zk_launch_dependent(head_gate_vec8_kernel, dim3((pieces + 255) / 256), dim3(256), 0, stream, (uint4*)rows, gate,
+                               ld_gate, pieces, H, width / 8);
+  }
   const int threads = 256, blocks = grid_for_total((size_t)n * H * width, threads);
   if (dtype == ZK_F32)
     return zk_launch_dependent(head_gate_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)rows, gate, ld_gate, n, H, width);

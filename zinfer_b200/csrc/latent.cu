@@ -13,7 +13,9 @@
 //     head's keys and values ARE expanded for the step's own tokens (one contraction of c against [W_uk; W_uv]),
 //     and (1b) latent_pack_kernel lays queries, keys and values out, padded to the widths the tensor-core prompt
 //     kernel takes, in rows ordered like a cache's pages for this step alone.  The scores then cost d + p
-//     multiplications a key, not r + p.
+//     multiplications a key, not r + p.  A prompt step that continues its sequences does the same over ALL their
+//     tokens: latent_gather_kernel packs the cached latents, the contraction expands them once more, and the shared
+//     key part is read back from the cache rows.
 // (2) head_gemm_kernel: out[t, h, :] = a[t, h, :] W[h]^T for few tokens, weights streamed once (the two per-head
 //     steps around attention in single-token steps), with an optional sigmoid gate per (token, head).
 #include "common.cuh"
@@ -79,55 +81,80 @@ __global__ void __launch_bounds__(LAT_THREADS)
   }
 }
 
-// One block per token of a prompt step whose sequences start at position 0.  q [n, H * (d + p)] as projected;
-// kvx rows `ld_kvx` apart: [H * d expanded unrotated keys | H * e expanded values]; dkv as above (its last p entries
-// are the shared key part before rotation).  Writes q_pad [n, H * HD] = [q_h[:d] | rot(q_h[d:]) | 0], and, at row
-// (page, h, pos % page_size) with page = seq_page0[sequence] + pos / page_size, k_rows [pages, H, page_size, HD] =
-// [k_h | rot(k_rot) | 0] and v_rows [pages, H, page_size, HDV] = [v_h | 0].
+// Queries, keys and values of a prompt step laid out for attention over rows of the step's own (no cache).
+// Block (t, 0), t < n_q: a step token.  q [n_q, H * (d + p)] as projected -> q_pad [n_q, H * HD] =
+// [q_h[:d] | rot(q_h[d:]) | 0], rotated by tok_pos[t].
+// Block (j, 1), j < n_kv: a key/value token (kv_seq[j], kv_pos[j]): the step's tokens themselves when its sequences
+// start at position 0, else every position of the step's sequences up to their last token.  kvx rows `ld_kvx` apart:
+// [H * d expanded unrotated keys | H * e expanded values] of token j.  The shared rotated key part comes from
+// dkv[j] (float32, rows `ld_dkv` apart, entries r.., rotated here) or, with `cache` given, from the token's cache row
+// (entries r.., already rotated).  Written at row (page, h, pos % page_size), page = seq_page0[sequence] + pos /
+// page_size: k_rows [pages, H, page_size, HD] = [k_h | rot(k_rot) | 0], v_rows [pages, H, page_size, HDV] = [v_h | 0].
 template <typename T>
 __global__ void __launch_bounds__(LAT_THREADS)
     latent_pack_kernel(const T* __restrict__ q, const T* __restrict__ kvx, int ld_kvx, const float* __restrict__ dkv,
                        int ld_dkv, const float* __restrict__ inv_freq, T* __restrict__ q_pad, T* __restrict__ k_rows,
-                       T* __restrict__ v_rows, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
-                       const int* __restrict__ seq_page0, int H, int d, int p, int e, int r, int HD, int HDV,
-                       int page_size) {
+                       T* __restrict__ v_rows, const int* __restrict__ tok_pos, const int* __restrict__ kv_seq,
+                       const int* __restrict__ kv_pos, const int* __restrict__ seq_page0, int n_q, int n_kv, int H, int d,
+                       int p, int e, int r, int HD, int HDV, int page_size, const T* __restrict__ cache,
+                       const int* __restrict__ seq_slot, const int* __restrict__ page_table, int pt_stride) {
   extern __shared__ float sh[];     // cos [p/2], sin [p/2], rotated shared key part [p]
   zk_let_next_start();
   zk_wait_prior();
   const int t = blockIdx.x, tid = threadIdx.x;
-  const int pos = tok_pos[t];
   const int half = p >> 1;
   float* cs = sh;
   float* sn = sh + half;
   float* kr = sh + p;
-  const float* src = dkv + (size_t)t * ld_dkv + r;
-  for (int i = tid; i < half; i += LAT_THREADS) {
-    const float ang = (float)pos * inv_freq[i];
-    const float c = cosf(ang), s = sinf(ang);
-    cs[i] = c;
-    sn[i] = s;
-    const float u = src[i], v = src[i + half];
-    kr[i] = u * c - v * s;
-    kr[i + half] = u * s + v * c;
+  const T zero = from_f32<T>(0.f);
+  if (blockIdx.y == 0) {
+    if (t >= n_q) return;
+    const int pos = tok_pos[t];
+    for (int i = tid; i < half; i += LAT_THREADS) {
+      const float ang = (float)pos * inv_freq[i];
+      cs[i] = cosf(ang);
+      sn[i] = sinf(ang);
+    }
+    __syncthreads();
+    for (int idx = tid; idx < H * HD; idx += LAT_THREADS) {
+      const int h = idx / HD, j = idx - h * HD;
+      const T* qh = q + ((size_t)t * H + h) * (d + p);
+      T qv = zero;
+      if (j < d) {
+        qv = qh[j];
+      } else if (j < d + p) {
+        const int i = j - d;
+        if (i < half) qv = from_f32<T>(to_f32(qh[d + i]) * cs[i] - to_f32(qh[d + i + half]) * sn[i]);
+        else qv = from_f32<T>(to_f32(qh[d + i - half]) * sn[i - half] + to_f32(qh[d + i]) * cs[i - half]);
+      }
+      q_pad[((size_t)t * H + h) * HD + j] = qv;
+    }
+    return;
+  }
+  if (t >= n_kv) return;
+  const int pos = kv_pos[t], b = kv_seq[t];
+  if (cache) {
+    const int cpage = page_table[(size_t)seq_slot[b] * pt_stride + pos / page_size];
+    const T* row = cache + ((size_t)(cpage < 0 ? 0 : cpage) * page_size + pos % page_size) * (r + p) + r;
+    for (int i = tid; i < p; i += LAT_THREADS) kr[i] = cpage < 0 ? 0.f : to_f32(row[i]);
+  } else {
+    const float* src = dkv + (size_t)t * ld_dkv + r;
+    for (int i = tid; i < half; i += LAT_THREADS) {
+      const float ang = (float)pos * inv_freq[i];
+      const float c = cosf(ang), s = sinf(ang);
+      const float u = src[i], v = src[i + half];
+      kr[i] = u * c - v * s;
+      kr[i + half] = u * s + v * c;
+    }
   }
   __syncthreads();
-  const size_t page = (size_t)seq_page0[tok_seq[t]] + pos / page_size;
+  const size_t page = (size_t)seq_page0[b] + pos / page_size;
   const int in_page = pos % page_size;
-  const T zero = from_f32<T>(0.f);
   for (int idx = tid; idx < H * HD; idx += LAT_THREADS) {
     const int h = idx / HD, j = idx - h * HD;
-    const T* qh = q + ((size_t)t * H + h) * (d + p);
-    T qv = zero, kv = zero;
-    if (j < d) {
-      qv = qh[j];
-      kv = kvx[(size_t)t * ld_kvx + (size_t)h * d + j];
-    } else if (j < d + p) {
-      const int i = j - d;
-      if (i < half) qv = from_f32<T>(to_f32(qh[d + i]) * cs[i] - to_f32(qh[d + i + half]) * sn[i]);
-      else qv = from_f32<T>(to_f32(qh[d + i - half]) * sn[i - half] + to_f32(qh[d + i]) * cs[i - half]);
-      kv = from_f32<T>(kr[i]);
-    }
-    q_pad[((size_t)t * H + h) * HD + j] = qv;
+    T kv = zero;
+    if (j < d) kv = kvx[(size_t)t * ld_kvx + (size_t)h * d + j];
+    else if (j < d + p) kv = from_f32<T>(kr[j - d]);
     k_rows[((page * H + h) * page_size + in_page) * HD + j] = kv;
   }
   for (int idx = tid; idx < H * HDV; idx += LAT_THREADS) {
@@ -135,6 +162,21 @@ __global__ void __launch_bounds__(LAT_THREADS)
     v_rows[((page * H + h) * page_size + in_page) * HDV + j] =
         j < e ? kvx[(size_t)t * ld_kvx + (size_t)H * d + (size_t)h * e + j] : zero;
   }
+}
+
+// c_all[j, :] = the first r entries of the cache row of key/value token (kv_seq[j], kv_pos[j]); zeros for a page
+// that is not there.  One block per token.
+template <typename T>
+__global__ void __launch_bounds__(LAT_THREADS)
+    latent_gather_kernel(const T* __restrict__ cache, T* __restrict__ c_all, const int* __restrict__ kv_seq,
+                         const int* __restrict__ kv_pos, const int* __restrict__ seq_slot,
+                         const int* __restrict__ page_table, int pt_stride, int r, int W, int page_size) {
+  zk_let_next_start();
+  zk_wait_prior();
+  const int j = blockIdx.x, pos = kv_pos[j];
+  const int page = page_table[(size_t)seq_slot[kv_seq[j]] * pt_stride + pos / page_size];
+  const T* row = cache + ((size_t)(page < 0 ? 0 : page) * page_size + pos % page_size) * W;
+  for (int i = threadIdx.x; i < r; i += LAT_THREADS) c_all[(size_t)j * r + i] = page < 0 ? from_f32<T>(0.f) : row[i];
 }
 
 // out[t, h, n] = (sum_k a[t, h, k] * w[h, n, k]) * (gate ? sigmoid(gate[t * ld_gate + h]) : 1).
@@ -203,23 +245,43 @@ int zk_latent_prepare(const void* q, void* q_full, const float* dkv, int ld_dkv,
 }
 
 int zk_latent_pack(const void* q, const void* kvx, int ld_kvx, const float* dkv, int ld_dkv, const float* inv_freq,
-                   void* q_pad, void* k_rows, void* v_rows, const int* tok_seq, const int* tok_pos, const int* seq_page0,
-                   int n_tokens, int H, int d, int p, int e, int r, int HD, int HDV, int page_size, int dtype,
+                   void* q_pad, void* k_rows, void* v_rows, const int* tok_pos, const int* kv_seq, const int* kv_pos,
+                   const int* seq_page0, int n_q, int n_kv, int H, int d, int p, int e, int r, int HD, int HDV,
+                   int page_size, const void* cache, const int* seq_slot, const int* page_table, int pt_stride, int dtype,
                    cudaStream_t stream) {
-  if (n_tokens <= 0) return 0;
+  if (n_q <= 0 && n_kv <= 0) return 0;
   if (H <= 0 || d <= 0 || p <= 0 || (p & 1) || e <= 0 || r <= 0 || HD < d + p || HDV < e || page_size <= 0 ||
-      ld_dkv < r + p || ld_kvx < H * (d + e))
+      ld_kvx < H * (d + e))
     return ZK_EINVAL;
+  if (cache ? (!seq_slot || !page_table) : (!dkv || ld_dkv < r + p)) return ZK_EINVAL;
   const size_t smem = sizeof(float) * 2 * (size_t)p;
   if (smem > 48 * 1024) return ZK_EINVAL;
+  const dim3 grid(n_q > n_kv ? n_q : n_kv, 2);
   if (dtype == ZK_F32)
-    return zk_launch_dependent(latent_pack_kernel<float>, dim3(n_tokens), dim3(LAT_THREADS), smem, stream, (const float*)q,
+    return zk_launch_dependent(latent_pack_kernel<float>, grid, dim3(LAT_THREADS), smem, stream, (const float*)q,
                                (const float*)kvx, ld_kvx, dkv, ld_dkv, inv_freq, (float*)q_pad, (float*)k_rows,
-                               (float*)v_rows, tok_seq, tok_pos, seq_page0, H, d, p, e, r, HD, HDV, page_size);
+                               (float*)v_rows, tok_pos, kv_seq, kv_pos, seq_page0, n_q, n_kv, H, d, p, e, r, HD, HDV,
+                               page_size, (const float*)cache, seq_slot, page_table, pt_stride);
   if (dtype == ZK_BF16)
-    return zk_launch_dependent(latent_pack_kernel<bf16>, dim3(n_tokens), dim3(LAT_THREADS), smem, stream, (const bf16*)q,
+    return zk_launch_dependent(latent_pack_kernel<bf16>, grid, dim3(LAT_THREADS), smem, stream, (const bf16*)q,
                                (const bf16*)kvx, ld_kvx, dkv, ld_dkv, inv_freq, (bf16*)q_pad, (bf16*)k_rows,
-                               (bf16*)v_rows, tok_seq, tok_pos, seq_page0, H, d, p, e, r, HD, HDV, page_size);
+                               (bf16*)v_rows, tok_pos, kv_seq, kv_pos, seq_page0, n_q, n_kv, H, d, p, e, r, HD, HDV,
+                               page_size, (const bf16*)cache, seq_slot, page_table, pt_stride);
+  return ZK_EINVAL;
+}
+
+// The latents of cached tokens, packed: c_all [n_kv, r] from cache [pages, 1, page_size, W].
+int zk_latent_gather(const void* cache, void* c_all, const int* kv_seq, const int* kv_pos, const int* seq_slot,
+                     const int* page_table, int pt_stride, int n_kv, int r, int W, int page_size, int dtype,
+                     cudaStream_t stream) {
+  if (n_kv <= 0) return 0;
+  if (r <= 0 || W < r || page_size <= 0) return ZK_EINVAL;
+  if (dtype == ZK_F32)
+    return zk_launch_dependent(latent_gather_kernel<float>, dim3(n_kv), dim3(LAT_THREADS), 0, stream, (const float*)cache,
+                               (float*)c_all, kv_seq, kv_pos, seq_slot, page_table, pt_stride, r, W, page_size);
+  if (dtype == ZK_BF16)
+    return zk_launch_dependent(latent_gather_kernel<bf16>, dim3(n_kv), dim3(LAT_THREADS), 0, stream, (const bf16*)cache,
+                               (bf16*)c_all, kv_seq, kv_pos, seq_slot, page_table, pt_stride, r, W, page_size);
   return ZK_EINVAL;
 }
 

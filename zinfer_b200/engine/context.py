@@ -64,8 +64,9 @@ class StepContext:
     """One step's batch on the device.  Built by the engine; parts only read it.
 
     n_tokens, n_seqs; q_lens (host list: tokens each sequence brings), max_q_len, max_kv_len
-    (longest sequence after the step), is_decode (one token for every sequence), from_start (every
-    sequence begins at position 0, so the step reads nothing that earlier steps cached); the device
+    (longest sequence after the step), is_decode (one token for every sequence), starts (host list of the
+    sequences' first positions in this step, or None) and from_start (every sequence begins at position 0, so the
+    step reads nothing that earlier steps cached); the device
     arrays tokens, tok_seq, tok_pos [n_tokens], cu_q [n_seqs + 1], seq_start, seq_slot [n_seqs];
     `status` (the device's status word), `sm_count`, and `host_tokens` (the ids on the host, or None).  `memo` keeps what parts derive from the
     batch's shape alone (tile tables and the like), so that equal parts derive it once a step; a
@@ -73,7 +74,7 @@ class StepContext:
 
     def __init__(self, dtype: torch.dtype, device, status: torch.Tensor, buf: torch.Tensor, n_tokens: int,
                  n_seqs: int, q_lens: Sequence[int], max_kv_len: int, memo: Optional[dict] = None,
-                 sm_count: int = 0, host_tokens: Optional[np.ndarray] = None, from_start: bool = False):
+                 sm_count: int = 0, host_tokens: Optional[np.ndarray] = None, starts: Optional[Sequence[int]] = None):
         self.dtype, self.device, self.status = dtype, device, status
         self.n_tokens, self.n_seqs = n_tokens, n_seqs
         self.q_lens = list(q_lens)
@@ -81,7 +82,10 @@ class StepContext:
         self.max_kv_len = max_kv_len
         self.is_decode = self.max_q_len == 1 and n_tokens == n_seqs
         self.sm_count = sm_count
-        self.from_start = bool(from_start)      # every sequence of the step begins at position 0: nothing cached is read
+        # where each sequence's tokens begin, as the host knows it (None: only the device does); from_start: every
+        # sequence of the step begins at position 0, so nothing cached is read.  Parts may plan with both, never need them.
+        self.starts = [int(s) for s in starts] if starts is not None else None
+        self.from_start = self.starts is not None and all(s == 0 for s in self.starts)
         # the step's token ids as the host packed them, or None when only the device knows them (a step that
         # runs on the tokens the step before sampled); parts may plan with them, never require them
         self.host_tokens = host_tokens

@@ -243,7 +243,7 @@ class Engine:
         buf = torch.from_numpy(host).pin_memory().to(self.device, non_blocking=True)
         max_kv = max(s + l for s, l in zip(starts, lens))
         ctx = StepContext(self.dtype, self.device, self.status, buf, n, B, lens, max_kv, sm_count=self.sm_count,
-                          host_tokens=host[:n], from_start=all(int(s) == 0 for s in starts))
+                          host_tokens=host[:n], starts=starts)
         cu = np.concatenate([[0], np.cumsum(lens)])
         rows = [int(cu[b]) + int(i) for b, w in enumerate(want) for i in w]
         if rows == list(range(n)):      # every row in order (a step of single tokens): no gather before the head

@@ -42,7 +42,8 @@ _SIGNATURES = {
     },
     "latent": {
         "zk_latent_prepare": "pppi" + "ppppppp" + "iiiiii" + "f" + "iii" + "ppp",
-        "zk_latent_pack": "ppipip" + "pppppp" + "iiiiiiiiii" + "p",
+        "zk_latent_pack": "ppipip" + "ppp" + "pppp" + "iiiiiiiiii" + "pppi" + "i" + "p",
+        "zk_latent_gather": "pppppp" + "iiiiii" + "p",
         "zk_head_gemm": "piippiipiiiiiip",
     },
     "hgrn2": {
@@ -1035,31 +1036,63 @@ def latent_prepare(q: torch.Tensor, q_full: torch.Tensor, dkv: torch.Tensor, c_w
         cache.shape[2], 1 if write_kv else 0, dtype_code(q.dtype), _ptr(status), _ptr(c_out), _stream()), "latent_prepare")
 
 
-def latent_pack(q: torch.Tensor, kvx: torch.Tensor, dkv: torch.Tensor, inv_freq: torch.Tensor, tok_seq, tok_pos,
+def latent_pack(q: torch.Tensor, kvx: torch.Tensor, dkv: Optional[torch.Tensor], inv_freq: torch.Tensor, tok_pos, kv_seq, kv_pos,
                 seq_page0: torch.Tensor, n_pages: int, page_size: int, n_heads: int, dim: int, rot_dim: int, value_dim: int,
-                rank: int, key_width: int, value_width: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Queries, keys and values of a prompt step that starts its sequences, for attention over the step's own rows.
-    q [n, H * (dim + rot_dim)] as projected; kvx [n, H * dim + H * value_dim]: every head's expanded unrotated keys,
-    then every head's values; dkv float32 [n, >= rank + rot_dim] (its entries rank.. are the shared key part before
-    rotation).  Returns q_pad [n, H * key_width] = [q_h[:dim] | rot(q_h[dim:]) | 0], k_rows [n_pages, H, page_size,
-    key_width] = [k_h | rot(k_rot) | 0] and v_rows [n_pages, H, page_size, value_width] = [v_h | 0], a token of
-    sequence b at position pos in page seq_page0[b] + pos // page_size."""
+                rank: int, key_width: int, value_width: int, cache: Optional[torch.Tensor] = None, seq_slot=None,
+                page_table=None) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Queries, keys and values of a prompt step, for attention over rows that the step lays out itself.
+    q [n, H * (dim + rot_dim)] as projected, tok_pos [n] the step tokens' positions; kvx [m, H * dim + H * value_dim]:
+    every head's expanded unrotated keys, then every head's values, of the m key/value tokens (kv_seq[j], kv_pos[j]):
+    the step's own tokens when its sequences start at position 0 (then dkv float32 [m, >= rank + rot_dim] holds the
+    shared key part before rotation in its entries rank..), or every position of the step's sequences (then `cache`
+    [pages, 1, page_size, rank + rot_dim] with `seq_slot` and `page_table` holds it, already rotated).  Returns q_pad
+    [n, H * key_width] = [q_h[:dim] | rot(q_h[dim:]) | 0], k_rows [n_pages, H, page_size, key_width] = [k_h | rot(k_rot)
+    | 0] and v_rows [n_pages, H, page_size, value_width] = [v_h | 0], a token of sequence b at position pos in page
+    seq_page0[b] + pos // page_size."""
     _need(q, "q", (torch.float32, torch.bfloat16), (None, n_heads * (dim + rot_dim)))
     n = q.shape[0]
-    _need(kvx, "kvx", q.dtype, (n, n_heads * (dim + value_dim)))
-    _need(dkv, "dkv", torch.float32, (n, None), contiguous=False)
-    if dkv.shape[1] < rank + rot_dim or dkv.stride(1) != 1:
-        raise KernelError(f"latent_pack: dkv {tuple(dkv.shape)} holds no {rank} + {rot_dim} values per row")
+    _need(kvx, "kvx", q.dtype, (None, n_heads * (dim + value_dim)))
+    m = kvx.shape[0]
+    ld_dkv = 0
+    if cache is None:
+        _need(dkv, "dkv", torch.float32, (m, None), contiguous=False)
+        if dkv.shape[1] < rank + rot_dim or dkv.stride(1) != 1:
+            raise KernelError(f"latent_pack: dkv {tuple(dkv.shape)} holds no {rank} + {rot_dim} values per row")
+        ld_dkv = dkv.stride(0)
+    else:
+        _need(cache, "cache", q.dtype, (None, 1, page_size, rank + rot_dim))
+        _need(page_table, "page_table", torch.int32, (None, None))
     _need(inv_freq, "inv_freq", torch.float32, (rot_dim // 2,))
     _need(seq_page0, "seq_page0", torch.int32, (None,))
+    _need(kv_seq, "kv_seq", torch.int32, (m,))
+    _need(kv_pos, "kv_pos", torch.int32, (m,))
     q_pad = torch.empty((n, n_heads * key_width), dtype=q.dtype, device=q.device)
     k_rows = torch.empty((n_pages, n_heads, page_size, key_width), dtype=q.dtype, device=q.device)
     v_rows = torch.empty((n_pages, n_heads, page_size, value_width), dtype=q.dtype, device=q.device)
     _check(_fn("latent", "zk_latent_pack")(
-        _ptr(q), _ptr(kvx), kvx.stride(0), _ptr(dkv), dkv.stride(0), _ptr(inv_freq), _ptr(q_pad), _ptr(k_rows), _ptr(v_rows),
-        _ptr(tok_seq), _ptr(tok_pos), _ptr(seq_page0), n, n_heads, dim, rot_dim, value_dim, rank, key_width, value_width,
-        page_size, dtype_code(q.dtype), _stream()), "latent_pack")
+        _ptr(q), _ptr(kvx), kvx.stride(0), _ptr(dkv) if cache is None else None, ld_dkv, _ptr(inv_freq), _ptr(q_pad),
+        _ptr(k_rows), _ptr(v_rows), _ptr(tok_pos), _ptr(kv_seq), _ptr(kv_pos), _ptr(seq_page0), n, m, n_heads, dim, rot_dim,
+        value_dim, rank, key_width, value_width, page_size, _ptr(cache), _ptr(seq_slot) if cache is not None else None,
+        _ptr(page_table) if cache is not None else None, page_table.stride(0) if cache is not None else 0,
+        dtype_code(q.dtype), _stream()), "latent_pack")
     return q_pad, k_rows, v_rows
+
+
+def latent_gather(cache: torch.Tensor, kv_seq, kv_pos, seq_slot, page_table, rank: int) -> torch.Tensor:
+    """c_all [m, rank]: the first `rank` entries of the cache rows of the tokens (kv_seq[j], kv_pos[j]); cache
+    [pages, 1, page_size, W]."""
+    _need(cache, "cache", (torch.float32, torch.bfloat16), (None, 1, None, None))
+    _need(kv_seq, "kv_seq", torch.int32, (None,))
+    m = kv_seq.numel()
+    _need(kv_pos, "kv_pos", torch.int32, (m,))
+    _need(page_table, "page_table", torch.int32, (None, None))
+    if rank > cache.shape[3]:
+        raise KernelError(f"latent_gather: rows of {cache.shape[3]} values hold no {rank}")
+    c_all = torch.empty((m, rank), dtype=cache.dtype, device=cache.device)
+    _check(_fn("latent", "zk_latent_gather")(_ptr(cache), _ptr(c_all), _ptr(kv_seq), _ptr(kv_pos), _ptr(seq_slot),
+                                             _ptr(page_table), page_table.stride(0), m, rank, cache.shape[3], cache.shape[2],
+                                             dtype_code(cache.dtype), _stream()), "latent_gather")
+    return c_all
 
 
 def head_gemm(a: torch.Tensor, a_head: int, w: torch.Tensor, out: torch.Tensor, o_head: int,

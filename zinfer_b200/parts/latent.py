@@ -20,6 +20,8 @@ A prompt step that starts its sequences reads nothing cached, and there the othe
 tokens get every head's k_h and v_h (one contraction of c against [W_uk; W_uv]), a kernel lays [k_h | k_rot] and v_h
 out in rows padded to the widths the tensor-core prompt kernel takes, and ordinary attention over those rows costs
 d + p multiplications a score instead of r + p.  The cache rows are written all the same, for the steps that follow.
+A prompt step that CONTINUES its sequences (a later portion of a long prompt) does the same over all their tokens:
+the cached latents are packed and expanded once more, and the shared key part is read back from the cache rows.
 
 The output gate is optional (`gate_name` None = none), as is the query latent (`q_down_name` None: q = W_uq h)."""
 from __future__ import annotations
@@ -33,6 +35,11 @@ from .. import kernels
 from .attention import key_chunks
 from .base import MIXERS, KVRequest, Mixer, WeightSpec
 from .linear import as_tensor, linear
+
+
+# A prompt step expands keys and values when it brings at least this share of its sequences' tokens: expanding costs a
+# contraction over ALL their tokens, which a step of a few tokens behind a long prompt would not earn back.
+EXPAND_MIN_SHARE = 1.0 / 16
 
 
 class LatentAttention(Mixer):
@@ -133,7 +140,8 @@ class LatentAttention(Mixer):
         q = linear(cq, self.w_uq)                                      # [n, H * (d + p)]
         dkv = low[:, :r + p]
         gate = low[:, r + p:r + p + H] if self.gate_name is not None else None
-        if (self.w_ukv is not None and ctx.from_start and not ctx.is_decode and call.writes_kv
+        if (self.w_ukv is not None and ctx.starts is not None and not ctx.is_decode and call.writes_kv
+                and ctx.n_tokens >= EXPAND_MIN_SHARE * sum(s + l for s, l in zip(ctx.starts, ctx.q_lens))
                 and kernels.attention_step_rows_takes(q.dtype, self.key_width, self.value_width, kv.page_size)):
             return self._forward_expanded(ctx, kv, q, dkv, gate, out, accumulate)
         q_full = torch.empty((n, H * (r + p)), dtype=q.dtype, device=q.device)
@@ -162,18 +170,35 @@ class LatentAttention(Mixer):
 
 
     def _forward_expanded(self, ctx, kv, q, dkv, gate, out, accumulate):
-        """A prompt step whose sequences start at position 0: keys and values expanded for the step's own tokens."""
+        """A prompt step whose host knows where its sequences begin: keys and values expanded for the step's own tokens
+        (sequences that start at position 0) or for every token of its sequences (a later portion of a prompt)."""
         H, d, p, e, r = self.n_heads, self.dim, self.rot_dim, self.value_dim, self.kv_rank
         n, page = ctx.n_tokens, kv.page_size
-        c = torch.empty((n, r), dtype=q.dtype, device=q.device)
+        c = torch.empty((n, r), dtype=q.dtype, device=q.device) if ctx.from_start else None
         kernels.latent_prepare(q, None, dkv, self.c_norm, self.inv_freq, kv.k, ctx.tok_seq, ctx.tok_pos, ctx.seq_slot,
                                kv.page_table, H, d, p, r, self.eps, ctx.status, write_kv=True, c_out=c)
-        kvx = linear(c, self.w_ukv)                                    # [n, H * d + H * e]
-        pages = [-(-l // page) for l in ctx.q_lens]
-        first = ctx.memo(("step pages", page), lambda: torch.from_numpy(
-            (np.cumsum([0] + pages[:-1])).astype(np.int32)).to(ctx.device, non_blocking=True))
-        q_pad, k_rows, v_rows = kernels.latent_pack(q, kvx, dkv, self.inv_freq, ctx.tok_seq, ctx.tok_pos, first, sum(pages), page,
-                                                    H, d, p, e, r, self.key_width, self.value_width)
+        ends = [s + l for s, l in zip(ctx.starts, ctx.q_lens)]
+        pages = [-(-t // page) for t in ends]
+
+        def tables():
+            words = [np.cumsum([0] + pages[:-1])]
+            if not ctx.from_start:      # every position of every sequence, in order
+                words += [np.repeat(np.arange(len(ends)), ends), np.concatenate([np.arange(t) for t in ends])]
+            dev = torch.from_numpy(np.concatenate(words).astype(np.int32)).to(ctx.device, non_blocking=True)
+            B, m = len(ends), sum(ends)
+            return (dev[:B], None, None) if ctx.from_start else (dev[:B], dev[B:B + m], dev[B + m:])
+
+        first, kv_seq, kv_pos = ctx.memo(("step rows", page), tables)
+        if ctx.from_start:
+            kvx = linear(c, self.w_ukv)                                # [n, H * d + H * e]
+            q_pad, k_rows, v_rows = kernels.latent_pack(q, kvx, dkv, self.inv_freq, ctx.tok_pos, ctx.tok_seq, ctx.tok_pos, first,
+                                                        sum(pages), page, H, d, p, e, r, self.key_width, self.value_width)
+        else:                           # the cache rows (this step's among them, just written) are expanded once more
+            c_all = kernels.latent_gather(kv.k, kv_seq, kv_pos, ctx.seq_slot, kv.page_table, r)
+            kvx = linear(c_all, self.w_ukv)
+            q_pad, k_rows, v_rows = kernels.latent_pack(q, kvx, None, self.inv_freq, ctx.tok_pos, kv_seq, kv_pos, first,
+                                                        sum(pages), page, H, d, p, e, r, self.key_width, self.value_width,
+                                                        cache=kv.k, seq_slot=ctx.seq_slot, page_table=kv.page_table)
         tile_tokens = kernels.attention_step_rows_tile_tokens(H)
         from .attention import GqaAttention
         tile_seq, tile_q0 = ctx.memo(("query tiles", tile_tokens), lambda: GqaAttention._tiles_on_device(ctx, tile_tokens))
