@@ -69,7 +69,7 @@ def expert_tensors(D, F, E, dtype, seed):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("D,F,E,top,rows", [(48, 24, 6, 2, 7), (64, 16, 4, 4, 33), (128, 64, 8, 2, 300), (128, 128, 3, 1, 200),
-                                            (38, 10, 5, 3, 130), (256, 96, 16, 2, 1)])
+                                            (38, 10, 5, 3, 130), (256, 96, 16, 2, 1), (128, 64, 8, 2, 700), (38, 10, 5, 2, 515)])
 def test_router_and_routed_experts_both_ways(k, dtype, D, F, E, top, rows):
     """The streaming kernels (few rows, single-token steps) and the grouped contractions (many rows), against the plain
     function; the router's ids and weights against the plain choice; rows alone against rows in a batch.  Rows whose
@@ -98,6 +98,8 @@ def test_router_and_routed_experts_both_ways(k, dtype, D, F, E, top, rows):
         outs[decode] = out - 0.5
         close(outs[decode][torch.from_numpy(keep).cuda()], ref[keep], dtype, "decode" if decode else "prompt")
     i = int(np.flatnonzero(keep)[-1])
+    ids1, wts1 = k.moe_router(x[i:i + 1].to(dtype).cuda(), ff.w_router, top)     # a row's choice is the same bits alone
+    assert torch.equal(ids1[0], ids[i]) and torch.equal(wts1[0], wts[i])
     alone = torch.zeros((1, D), device="cuda")
     ff.forward(Ctx(k, dtype, 1, True), x[i:i + 1].to(dtype).cuda(), alone, False)
     assert torch.equal(alone[0], (outs[True][i] + 0.5) - 0.5) or torch.allclose(alone[0], outs[True][i], atol=1e-6)
