@@ -59,7 +59,7 @@ CONFIGS = {
     "kc": {"architecture": "Kerotar", "vocab": 512, "width": 128, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
            "loop": {"start": 1, "stop": 3, "times": 2},
            "layers": [_latent(4, 32, 32, 64, 64, 64, 0.12, 10000.0, mlp=_dense(256, 1.0)),
-                      _attn(8, 2, 64, 64, 0.12, rot=(250000.0, 32), mask=(96, 5), mlp=_moe(8, 2, 64)),
+                      _attn(8, 2, 64, 64, 0.12, rot=(300000.0, 32), mask=(112, 5), mlp=_moe(8, 2, 64)),
                       _attn(4, 4, 64, 64, 0.11, rot=(500.0, 64), mlp=_moe(3, 1, 128)),
                       _latent(2, 64, 16, 32, 128, 96, 0.1, 1000.0)]},
     # the least there can be: one latent layer with one head and no feed-forward, in a loop that runs once

@@ -22,7 +22,7 @@ def test_configuration_reads_every_key_and_round_trips():
         assert c.to_json_dict() == d, name
         assert dataclasses.replace(z.config_from_dict(c.to_json_dict()), raw={}) == dataclasses.replace(c, raw={})
     c = z.config_from_dict(H.CONFIGS["kc"])
-    assert c.layers[2].mixer.window == 0 and c.layers[1].mixer.keep_first == 5 and c.layers[1].mixer.window == 96
+    assert c.layers[2].mixer.window == 0 and c.layers[1].mixer.keep_first == 5 and c.layers[1].mixer.window == 112
     assert c.layers[3].mlp is None and c.layers[2].mlp.top == 1 and c.layers[0].mlp.limit == 1.0
     assert c.layers[0].mixer.kv_rank == 64 and c.layers[3].mixer.rot_dim == 16 and c.loop.times == 2
     d = copy.deepcopy(H.CONFIGS["kb"])

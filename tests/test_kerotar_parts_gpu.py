@@ -200,7 +200,7 @@ def plain_window(x, t, H, G, d, vd, scale, rot, mask, eps=2e-6):
 @pytest.mark.parametrize("D,H,G,d,vd,scale,rot,mask,page", [
     (40, 4, 2, 16, 12, 0.3, (100.0, 8), (20, 3), 16),          # window over a page border, three kept tokens
     (64, 6, 6, 8, 16, 0.35, (30.0, 4), (7, 20), 16),           # more kept tokens than the window is long, in two pages
-    (128, 8, 2, 64, 64, 0.12, (250000.0, 32), (96, 5), 64),    # head widths the tensor cores take
+    (128, 8, 2, 64, 64, 0.12, (300000.0, 32), (112, 5), 64),   # head widths the tensor cores take
     (128, 4, 4, 64, 64, 0.11, (500.0, 64), None, 64),          # no window at all: the sink alone
     (38, 5, 5, 10, 7, 0.3, (20.0, 6), (33, 1), 16),            # odd sizes, one kept token
     (64, 2, 1, 32, 32, 0.2, None, (40, 0), 32),                # a window without kept tokens and without rotation

@@ -97,7 +97,8 @@ __global__ void __launch_bounds__(LAT_THREADS)
                        T* __restrict__ v_rows, const int* __restrict__ tok_pos, const int* __restrict__ kv_seq,
                        const int* __restrict__ kv_pos, const int* __restrict__ seq_page0, int n_q, int n_kv, int H, int d,
                        int p, int e, int r, int HD, int HDV, int page_size, const T* __restrict__ cache,
-                       const int* __restrict__ seq_slot, const int* __restrict__ page_table, int pt_stride) {
+                       const int* __restrict__ seq_slot, const int* __restrict__ page_table, int pt_stride, int vec8) {
+  // vec8: rows are moved in 16-byte pieces (bfloat16; d, p, e, HD, HDV, ld_kvx multiples of 8 and 16-byte aligned bases)
   extern __shared__ float sh[];     // cos [p/2], sin [p/2], rotated shared key part [p]
   zk_let_next_start();
   zk_wait_prior();
@@ -116,6 +117,28 @@ __global__ void __launch_bounds__(LAT_THREADS)
       sn[i] = sinf(ang);
     }
     __syncthreads();
+    if (sizeof(T) == 2 && vec8) {        // whole 16-byte pieces: a piece lies in one of the three parts of a row
+      const int CH = HD / 8;
+      for (int idx = tid; idx < H * CH; idx += LAT_THREADS) {
+        const int h = idx / CH, j0 = (idx - h * CH) * 8;
+        const T* qh = q + ((size_t)t * H + h) * (d + p);
+        uint4 piece = make_uint4(0u, 0u, 0u, 0u);
+        if (j0 < d) {
+          piece = *reinterpret_cast<const uint4*>(qh + j0);
+        } else if (j0 < d + p) {
+          __align__(16) T vals[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int i = j0 - d + u;
+            vals[u] = i < half ? from_f32<T>(to_f32(qh[d + i]) * cs[i] - to_f32(qh[d + i + half]) * sn[i])
+                               : from_f32<T>(to_f32(qh[d + i - half]) * sn[i - half] + to_f32(qh[d + i]) * cs[i - half]);
+          }
+          piece = *reinterpret_cast<const uint4*>(vals);
+        }
+        *reinterpret_cast<uint4*>(q_pad + ((size_t)t * H + h) * HD + j0) = piece;
+      }
+      return;
+    }
     for (int idx = tid; idx < H * HD; idx += LAT_THREADS) {
       const int h = idx / HD, j = idx - h * HD;
       const T* qh = q + ((size_t)t * H + h) * (d + p);
@@ -150,6 +173,29 @@ __global__ void __launch_bounds__(LAT_THREADS)
   __syncthreads();
   const size_t page = (size_t)seq_page0[b] + pos / page_size;
   const int in_page = pos % page_size;
+  if (sizeof(T) == 2 && vec8) {
+    const int CH = HD / 8, CHV = HDV / 8;
+    for (int idx = tid; idx < H * CH; idx += LAT_THREADS) {
+      const int h = idx / CH, j0 = (idx - h * CH) * 8;
+      uint4 piece = make_uint4(0u, 0u, 0u, 0u);
+      if (j0 < d) {
+        piece = *reinterpret_cast<const uint4*>(kvx + (size_t)t * ld_kvx + (size_t)h * d + j0);
+      } else if (j0 < d + p) {
+        __align__(16) T vals[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) vals[u] = from_f32<T>(kr[j0 - d + u]);
+        piece = *reinterpret_cast<const uint4*>(vals);
+      }
+      *reinterpret_cast<uint4*>(k_rows + ((page * H + h) * page_size + in_page) * HD + j0) = piece;
+    }
+    for (int idx = tid; idx < H * CHV; idx += LAT_THREADS) {
+      const int h = idx / CHV, j0 = (idx - h * CHV) * 8;
+      uint4 piece = make_uint4(0u, 0u, 0u, 0u);
+      if (j0 < e) piece = *reinterpret_cast<const uint4*>(kvx + (size_t)t * ld_kvx + (size_t)H * d + (size_t)h * e + j0);
+      *reinterpret_cast<uint4*>(v_rows + ((page * H + h) * page_size + in_page) * HDV + j0) = piece;
+    }
+    return;
+  }
   for (int idx = tid; idx < H * HD; idx += LAT_THREADS) {
     const int h = idx / HD, j = idx - h * HD;
     T kv = zero;
@@ -257,16 +303,18 @@ int zk_latent_pack(const void* q, const void* kvx, int ld_kvx, const float* dkv,
   const size_t smem = sizeof(float) * 2 * (size_t)p;
   if (smem > 48 * 1024) return ZK_EINVAL;
   const dim3 grid(n_q > n_kv ? n_q : n_kv, 2);
+  const int vec8 = dtype == ZK_BF16 && !((d | p | e | HD | HDV | ld_kvx) & 7) &&
+                   !(((uintptr_t)q | (uintptr_t)kvx | (uintptr_t)q_pad | (uintptr_t)k_rows | (uintptr_t)v_rows) & 15);
   if (dtype == ZK_F32)
     return zk_launch_dependent(latent_pack_kernel<float>, grid, dim3(LAT_THREADS), smem, stream, (const float*)q,
                                (const float*)kvx, ld_kvx, dkv, ld_dkv, inv_freq, (float*)q_pad, (float*)k_rows,
                                (float*)v_rows, tok_pos, kv_seq, kv_pos, seq_page0, n_q, n_kv, H, d, p, e, r, HD, HDV,
-                               page_size, (const float*)cache, seq_slot, page_table, pt_stride);
+                               page_size, (const float*)cache, seq_slot, page_table, pt_stride, 0);
   if (dtype == ZK_BF16)
     return zk_launch_dependent(latent_pack_kernel<bf16>, grid, dim3(LAT_THREADS), smem, stream, (const bf16*)q,
                                (const bf16*)kvx, ld_kvx, dkv, ld_dkv, inv_freq, (bf16*)q_pad, (bf16*)k_rows,
                                (bf16*)v_rows, tok_pos, kv_seq, kv_pos, seq_page0, n_q, n_kv, H, d, p, e, r, HD, HDV,
-                               page_size, (const bf16*)cache, seq_slot, page_table, pt_stride);
+                               page_size, (const bf16*)cache, seq_slot, page_table, pt_stride, vec8);
   return ZK_EINVAL;
 }
 

@@ -249,62 +249,43 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
   }
 }
 
-// Router of a mixture of experts, one block per TB tokens.  The logits are float32 dot products (a warp per expert,
-// lanes striding the row, sums in lane order then the warp's tree; a weight is read once for the block's TB tokens, and
-// a token's sum is the same whatever TB is), the softmax runs over all E experts, and warp i then picks the `top`
-// largest scores of the block's token i one after the other (of equal scores the lower index first).
+// Router of a mixture of experts, one block per token.  The logits are float32 dot products (a warp per expert,
+// lanes striding the row, sums in lane order then the warp's tree), the softmax runs over all E experts, and warp 0
+// then picks the `top` largest scores one after the other (of equal scores the lower index first).
 #define MOE_ROUTER_MAX_EXPERTS 4096
-template <typename T, int TB>
+template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
     moe_router_kernel(const T* __restrict__ x, const float* __restrict__ w, int* __restrict__ ids, float* __restrict__ wts,
-                      int n, int D, int E, int top) {
-  static_assert(TB <= MOE_WARPS, "a warp per token picks the experts");
-  extern __shared__ float rs[];     // [TB][D] the tokens' rows, [TB][E] logits then scores
+                      int D, int E, int top) {
+  extern __shared__ float rs[];     // [D] the token's row, [E] logits then scores
   float* xs = rs;
-  float* zs = rs + (size_t)TB * D;
+  float* z = rs + D;
   zk_let_next_start();
   zk_wait_prior();
-  const int t0 = blockIdx.x * TB, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < TB * D; i += blockDim.x) {
-    const int tb = i / D, d = i - tb * D;
-    xs[i] = t0 + tb < n ? to_f32(x[(size_t)(t0 + tb) * D + d]) : 0.f;
-  }
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) xs[d] = to_f32(x[(size_t)t * D + d]);
   __syncthreads();
   for (int e = warp; e < E; e += MOE_WARPS) {
     const float* wr = w + (size_t)e * D;
-    float acc[TB];
-#pragma unroll
-    for (int tb = 0; tb < TB; ++tb) acc[tb] = 0.f;
+    float acc = 0.f;
     if ((D & 3) == 0) {          // rows in pieces of four: a quarter of the loads (D is the model's: one order per model)
       const float4* w4 = reinterpret_cast<const float4*>(wr);
+      const float4* x4 = reinterpret_cast<const float4*>(xs);
       for (int d = lane; d < (D >> 2); d += 32) {
-        const float4 a = w4[d];
-#pragma unroll
-        for (int tb = 0; tb < TB; ++tb) {
-          const float4 v = reinterpret_cast<const float4*>(xs + (size_t)tb * D)[d];
-          acc[tb] = fmaf(a.x, v.x, acc[tb]);
-          acc[tb] = fmaf(a.y, v.y, acc[tb]);
-          acc[tb] = fmaf(a.z, v.z, acc[tb]);
-          acc[tb] = fmaf(a.w, v.w, acc[tb]);
-        }
+        const float4 a = w4[d], v = x4[d];
+        acc = fmaf(a.x, v.x, acc);
+        acc = fmaf(a.y, v.y, acc);
+        acc = fmaf(a.z, v.z, acc);
+        acc = fmaf(a.w, v.w, acc);
       }
     } else {
-      for (int d = lane; d < D; d += 32) {
-        const float a = wr[d];
-#pragma unroll
-        for (int tb = 0; tb < TB; ++tb) acc[tb] = fmaf(a, xs[(size_t)tb * D + d], acc[tb]);
-      }
+      for (int d = lane; d < D; d += 32) acc = fmaf(wr[d], xs[d], acc);
     }
-#pragma unroll
-    for (int tb = 0; tb < TB; ++tb) {
-      const float v = warp_sum(acc[tb]);
-      if (lane == 0) zs[tb * E + e] = v;
-    }
+    acc = warp_sum(acc);
+    if (lane == 0) z[e] = acc;
   }
   __syncthreads();
-  if (warp >= TB || t0 + warp >= n) return;
-  const int t = t0 + warp;
-  float* z = zs + warp * E;
+  if (warp != 0) return;
   float m = -INFINITY;
   for (int e = lane; e < E; e += 32) m = fmaxf(m, z[e]);
   m = warp_max(m);
@@ -435,30 +416,20 @@ int zk_moe_router(const void* x, const float* w_router, int* route_ids, float* r
                   int dtype, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (D <= 0 || E <= 0 || top <= 0 || top > E || E > MOE_ROUTER_MAX_EXPERTS) return ZK_EINVAL;
-  // prompt steps: 8 (or 4) tokens a block read each router row once; few tokens: a block each, so that all are at work
-  const size_t per_token = sizeof(float) * ((size_t)D + E);
-  if (per_token > 200 * 1024) return ZK_EINVAL;
-  const int tb = n >= 512 && 8 * per_token <= 96 * 1024 ? 8 : (n >= 512 && 4 * per_token <= 96 * 1024 ? 4 : 1);
-  const size_t smem = per_token * tb;
-#define ZK_ROUTER_TB(T, TBV)                                                                                         \
+  const size_t smem = sizeof(float) * ((size_t)D + E);
+  if (smem > 200 * 1024) return ZK_EINVAL;
+#define ZK_ROUTER(T)                                                                                                 \
   do {                                                                                                               \
-    auto kern = moe_router_kernel<T, TBV>;                                                                           \
+    auto kern = moe_router_kernel<T>;                                                                                \
     if (smem > 48 * 1024) {                                                                                          \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
       if (e != cudaSuccess) return (int)e;                                                                           \
     }                                                                                                                \
-    return zk_launch_dependent(kern, dim3((n + TBV - 1) / TBV), dim3(MOE_WARPS * 32), smem, stream, (const T*)x,     \
-                               w_router, route_ids, route_w, n, D, E, top);                                          \
-  } while (0)
-#define ZK_ROUTER(T)                 \
-  do {                               \
-    if (tb == 8) ZK_ROUTER_TB(T, 8); \
-    if (tb == 4) ZK_ROUTER_TB(T, 4); \
-    ZK_ROUTER_TB(T, 1);              \
+    return zk_launch_dependent(kern, dim3(n), dim3(MOE_WARPS * 32), smem, stream, (const T*)x, w_router, route_ids,  \
+                               route_w, D, E, top);                                                                  \
   } while (0)
   if (dtype == ZK_F32) ZK_ROUTER(float);
   if (dtype == ZK_BF16) ZK_ROUTER(bf16);
-#undef ZK_ROUTER_TB
 #undef ZK_ROUTER
   return ZK_EINVAL;
 }
