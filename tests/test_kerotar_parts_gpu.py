@@ -322,6 +322,8 @@ def plain_latent(x, t, H, d, p, e, r, s, scale, base, eps=2e-6):
     (128, 3, 32, 16, 96, 80, 64, 0.14, 500.0, 64),            # values wider than the keys
     (128, 20, 16, 32, 16, 512, 48, 0.1, 10000.0, 64),         # rows of 544 values, heads in two groups of sixteen
     (64, 17, 16, 16, 32, 272, 32, 0.15, 100.0, 64),           # rows of 288 values, one head beyond the first group
+    (96, 3, 20, 12, 28, 40, 36, 0.18, 300.0, 64),             # pages of 64 with widths that are no multiples of 8 or 16
+    (80, 5, 10, 6, 70, 24, 30, 0.25, 50.0, 64),               # values of 70 in rows of 128, keys of 16 in rows of 128
 ])
 def test_latent_attention_alone(k, dtype, D, H, d, p, e, r, s, scale, base, page):
     t = latent_tensors(D, H, d, p, e, r, s, dtype, 70)
@@ -339,7 +341,7 @@ def test_latent_attention_alone(k, dtype, D, H, d, p, e, r, s, scale, base, page
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("D,H,d,p,e,r,s,page", [(128, 4, 32, 32, 64, 64, 64, 64), (128, 2, 64, 32, 64, 160, 64, 64),
-                                                (64, 3, 16, 8, 20, 48, 40, 16)])
+                                                (64, 3, 16, 8, 20, 48, 40, 16), (96, 3, 20, 12, 28, 40, 36, 64)])
 def test_latent_attention_in_portions_of_a_prompt(k, dtype, D, H, d, p, e, r, s, page):
     """Two sequences whose prompts come in portions of unequal sizes (a long later portion, which expands the cached
     latents once more; a short one behind a long prefix; portions of two tokens; a portion that ends on a page border)."""
