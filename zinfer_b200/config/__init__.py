@@ -3,5 +3,6 @@ from .lfm2 import Lfm2Config
 from .ponusun import PonusunConfig
 from .zosurax import ZosuraxConfig
 from .kerotar import KerotarConfig
+from .pirisun import PirisunConfig
 from .registry import (architecture_name, build_model, config_from_dict, config_from_folder, get_architecture,
                        register_architecture, registered_architectures, unregister_architecture)

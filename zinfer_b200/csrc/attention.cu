@@ -26,6 +26,10 @@
 // With `dense_out` the results of all three kinds go to a dense [n, (H + 2 Hkv) * hd] tensor
 // instead (no cache write): the first half of a two-step path for position encodings that
 // are not a rotation table.
+__device__ __forceinline__ float query_temperature(int pos, float coef, int every) {
+  return 1.0f + coef * logf((float)((pos + 1) / every + 1));
+}
+
 template <typename T>
 __global__ void qk_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ dense_out,
                                   T* __restrict__ k_cache,
@@ -34,10 +38,11 @@ __global__ void qk_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
                                   const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
                                   const int* __restrict__ page_table, int pt_stride, int n_tokens, int H, int Hkv,
                                   int hd, int n_rot, int interleaved, float eps, int page_size, int write_kv,
-                                  int* status, int vd, int unit_norm_after) {
+                                  int* status, int vd, int unit_norm_after, float qt_coef, int qt_every) {
   // vd: width of a value head (a row of qkv is [q H*hd | k Hkv*hd | v Hkv*vd]).  unit_norm_after: q and k
   // heads are divided by their root mean square (no weight) AFTER the rotation; q_w / k_w, if given,
-  // weigh an RMS norm BEFORE it.
+  // weigh an RMS norm BEFORE it.  qt_every > 0: a query at position p is multiplied, last of all, by
+  // 1 + qt_coef * ln(floor((p + 1) / qt_every) + 1) (a temperature that grows with the position), in float32.
   __shared__ float sm_all[ATT_WARPS][ATT_MAX_HD];
   zk_wait_prior();   // nothing of the kernels before is read, and nothing written, above this line
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -88,6 +93,11 @@ __global__ void qk_prepare_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
     for (int d = lane; d < hd; d += 32) sm[d] *= scale;
     __syncwarp();
   }
+  if (kind == 0 && qt_every > 0) {
+    const float temp = query_temperature(pos, qt_coef, qt_every);
+    for (int d = lane; d < hd; d += 32) sm[d] *= temp;
+    __syncwarp();
+  }
   T* dst;
   if (dense_out) {
     dst = dense_out + (size_t)t * row_w + col0;
@@ -119,7 +129,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
                             const float* __restrict__ inv_freq, const int* __restrict__ tok_seq,
                             const int* __restrict__ tok_pos, const int* __restrict__ seq_slot,
                             const int* __restrict__ page_table, int pt_stride, int H, int Hkv, float eps, int page_size,
-                            int write_kv, int* status) {
+                            int write_kv, int* status, float qt_coef, int qt_every) {
   constexpr int E = HD / 64, HALF = HD / 2;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x;
@@ -134,6 +144,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
     cs[e] = cosf(ang);
     sn[e] = sinf(ang);
   }
+  const float temp = qt_every > 0 ? query_temperature(pos, qt_coef, qt_every) : 1.0f;
   int page = -2;   // not looked up yet
   const int n_slots = write_kv ? slots : H;
   // A warp's head slots four at a time: their loads are all under way before the first is used.
@@ -188,6 +199,13 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
       }
       T* dst;
       if (kind == 0) {
+        if (qt_every > 0) {
+#pragma unroll
+          for (int e = 0; e < E; ++e) {
+            a[e] *= temp;
+            b[e] *= temp;
+          }
+        }
         dst = q_out + (size_t)t * H * HD + (size_t)s * HD;
       } else {
         if (page == -2) page = page_table[(size_t)seq_slot[tok_seq[t]] * pt_stride + pos / page_size];
@@ -341,7 +359,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
                     const int* __restrict__ page_table, int pt_stride, int n_tokens, int H, int Hkv, int hd,
                     int page_size, int window, float scale, int bq, int gc, int num_splits, int split_keys, int vd,
                     const float* __restrict__ bias_r1, const float* __restrict__ bias_r2, int cross, int keep,
-                    const float* __restrict__ sink, int v_from_k) {
+                    const float* __restrict__ sink, int v_from_k, float softcap) {
+  // softcap > 0: a scaled score s becomes softcap * tanh(s / softcap) before anything else is done with it.
   // keep: with a window, the first `keep` positions of a sequence stay visible to every later query.
   // sink [H]: exp(sink_h) is one more term of head h's softmax denominator (no key, no value, unscaled).
   // v_from_k: a value row is the first vd entries of the key row (one vector per token serves as both).
@@ -472,6 +491,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
       float sc = -INFINITY;
       if (ok) {
         sc = s[i] * scale;
+        if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
         if (biased) sc -= r1[i] * log1pf(r2[i] * (float)(row_hi[i] - 1 - kp));
       }
       const float mt = warp_max(sc);
@@ -707,7 +727,7 @@ int launch_attn(const void* q, const void* k_cache, const void* v_cache, void* o
                 const int* tile_seq, const int* tile_q0, const int* cu_q, const int* seq_start, const int* seq_slot,
                 const int* page_table, int pt_stride, int n_tiles, int n_tokens, int H, int Hkv, int hd, int page_size,
                 int window, float scale, int bq, int gc, int num_splits, int split_keys, int vd, const float* r1,
-                const float* r2, int cross, int keep, const float* sink, int v_from_k, cudaStream_t stream) {
+                const float* r2, int cross, int keep, const float* sink, int v_from_k, float softcap, cudaStream_t stream) {
   const size_t smem = attn_smem_bytes(hd, v_from_k ? 0 : vd);
   if (smem > 227 * 1024) return ZK_EINVAL;
   auto kern = attn_fwd_kernel<T, NPL>;
@@ -721,7 +741,7 @@ int launch_attn(const void* q, const void* k_cache, const void* v_cache, void* o
   kern<<<grid, ATT_WARPS * 32, smem, stream>>>((const T*)q, (const T*)k_cache, (const T*)v_cache, (T*)out, part_o,
                                                part_ml, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table,
                                                pt_stride, n_tokens, H, Hkv, hd, page_size, window, scale, bq, gc,
-                                               num_splits, split_keys, vd, r1, r2, cross, keep, sink, v_from_k);
+                                               num_splits, split_keys, vd, r1, r2, cross, keep, sink, v_from_k, softcap);
   return ZK_LAUNCH_STATUS();
 }
 
@@ -730,13 +750,13 @@ int dispatch_attn(int hd, const void* q, const void* k_cache, const void* v_cach
                   float* part_ml, const int* tile_seq, const int* tile_q0, const int* cu_q, const int* seq_start,
                   const int* seq_slot, const int* page_table, int pt_stride, int n_tiles, int n_tokens, int H, int Hkv,
                   int page_size, int window, float scale, int bq, int gc, int num_splits, int split_keys, int vd,
-                  const float* r1, const float* r2, int cross, int keep, const float* sink, int v_from_k,
+                  const float* r1, const float* r2, int cross, int keep, const float* sink, int v_from_k, float softcap,
                   cudaStream_t stream) {
 #define ZK_ATT_CASE(N)                                                                                               \
   case N:                                                                                                            \
     return launch_attn<T, N>(q, k_cache, v_cache, out, part_o, part_ml, tile_seq, tile_q0, cu_q, seq_start, seq_slot, \
                              page_table, pt_stride, n_tiles, n_tokens, H, Hkv, hd, page_size, window, scale, bq, gc,  \
-                             num_splits, split_keys, vd, r1, r2, cross, keep, sink, v_from_k, stream);
+                             num_splits, split_keys, vd, r1, r2, cross, keep, sink, v_from_k, softcap, stream);
   int npl = (vd + 31) / 32;                 // value columns per lane: every count up to 8, then 12, 16, 20
   if (npl > 8) npl = npl <= 12 ? 12 : (npl <= 16 ? 16 : 20);
   switch (npl) {
@@ -760,7 +780,7 @@ int zk_qk_prepare(const void* qkv, void* q_out, void* dense_out, void* k_cache, 
                   const float* inv_freq, const int* tok_seq, const int* tok_pos, const int* seq_slot,
                   const int* page_table, int pt_stride, int n_tokens, int H, int Hkv, int hd, int n_rot,
                   int interleaved, float eps, int page_size, int write_kv, int dtype, int* status, int vd,
-                  int unit_norm_after, cudaStream_t stream) {
+                  int unit_norm_after, float qt_coef, int qt_every, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (hd <= 0 || hd > ATT_MAX_HD || H <= 0 || Hkv <= 0 || n_rot > hd || (n_rot & 1) || page_size <= 0) return ZK_EINVAL;
   if (vd <= 0) vd = hd;
@@ -772,7 +792,7 @@ int zk_qk_prepare(const void* qkv, void* q_out, void* dense_out, void* k_cache, 
 #define ZK_QKP(T, HDV)                                                                                               \
   zk_launch_dependent(qk_prepare_token_kernel<T, HDV>, dim3(n_tokens), dim3(ATT_WARPS * 32), 0, stream,             \
       (const T*)qkv, (T*)q_out, (T*)k_cache, (T*)v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos, seq_slot, page_table, \
-      pt_stride, H, Hkv, eps, page_size, write_kv, status)
+      pt_stride, H, Hkv, eps, page_size, write_kv, status, qt_coef, qt_every)
     if (dtype == ZK_F32 && hd == 64) ZK_QKP(float, 64);
     else if (dtype == ZK_F32) ZK_QKP(float, 128);
     else if (hd == 64) ZK_QKP(bf16, 64);
@@ -786,12 +806,12 @@ int zk_qk_prepare(const void* qkv, void* q_out, void* dense_out, void* k_cache, 
     return zk_launch_dependent(qk_prepare_kernel<float>, dim3(blocks), dim3(ATT_WARPS * 32), 0, stream,
         (const float*)qkv, (float*)q_out, (float*)dense_out, (float*)k_cache, (float*)v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos,
         seq_slot, page_table, pt_stride, n_tokens, H, Hkv, hd, n_rot, interleaved, eps, page_size, write_kv, status, vd,
-        unit_norm_after);
+        unit_norm_after, qt_coef, qt_every);
   else if (dtype == ZK_BF16)
     return zk_launch_dependent(qk_prepare_kernel<bf16>, dim3(blocks), dim3(ATT_WARPS * 32), 0, stream,
         (const bf16*)qkv, (bf16*)q_out, (bf16*)dense_out, (bf16*)k_cache, (bf16*)v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos, seq_slot,
         page_table, pt_stride, n_tokens, H, Hkv, hd, n_rot, interleaved, eps, page_size, write_kv, status, vd,
-        unit_norm_after);
+        unit_norm_after, qt_coef, qt_every);
   else
     return ZK_EINVAL;
   return ZK_LAUNCH_STATUS();
@@ -840,7 +860,7 @@ int zk_attn_fwd(const void* q, const void* k_cache, const void* v_cache, void* o
                 const int* page_table, int pt_stride, int n_tiles, int n_tokens, int H, int Hkv, int hd, int page_size,
                 int window, float scale, int bq, int gc, int num_splits, int split_keys, int dtype, int vd,
                 const float* bias_r1, const float* bias_r2, int cross, int keep, const float* sink, int v_from_k,
-                cudaStream_t stream) {
+                float softcap, cudaStream_t stream) {
   if (n_tiles <= 0 || n_tokens <= 0) return 0;
   if (keep < 0 || (v_from_k && (vd > hd || cross))) return ZK_EINVAL;
   if (cross && (!part_o || !part_ml)) return ZK_EINVAL;
@@ -851,11 +871,11 @@ int zk_attn_fwd(const void* q, const void* k_cache, const void* v_cache, void* o
   if (dtype == ZK_F32)
     return dispatch_attn<float>(hd, q, k_cache, v_cache, out, part_o, part_ml, tile_seq, tile_q0, cu_q, seq_start,
                                 seq_slot, page_table, pt_stride, n_tiles, n_tokens, H, Hkv, page_size, window, scale,
-                                bq, gc, num_splits, split_keys, vd, bias_r1, bias_r2, cross, keep, sink, v_from_k, stream);
+                                bq, gc, num_splits, split_keys, vd, bias_r1, bias_r2, cross, keep, sink, v_from_k, softcap, stream);
   if (dtype == ZK_BF16)
     return dispatch_attn<bf16>(hd, q, k_cache, v_cache, out, part_o, part_ml, tile_seq, tile_q0, cu_q, seq_start,
                                seq_slot, page_table, pt_stride, n_tiles, n_tokens, H, Hkv, page_size, window, scale, bq,
-                               gc, num_splits, split_keys, vd, bias_r1, bias_r2, cross, keep, sink, v_from_k, stream);
+                               gc, num_splits, split_keys, vd, bias_r1, bias_r2, cross, keep, sink, v_from_k, softcap, stream);
   return ZK_EINVAL;
 }
 

@@ -68,7 +68,8 @@ __global__ void __launch_bounds__(DL_THREADS)
     attn_decode_latent_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, bf16* __restrict__ out,
                               float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ seq_start,
                               const int* __restrict__ seq_slot, const int* __restrict__ page_table, int pt_stride,
-                              int n_seqs, int H, int W, int R, int page_size, float scale, int num_splits, int split_keys) {
+                              int n_seqs, int H, int W, int R, int page_size, float scale, int num_splits, int split_keys,
+                              int parts_always) {
   const int RS = padded_row(W);                       // row stride in shared memory, bfloat16
   const int CHW = W / 8;                              // 16-byte pieces of a row
   extern __shared__ __align__(128) unsigned char smem[];
@@ -231,13 +232,13 @@ __global__ void __launch_bounds__(DL_THREADS)
     for (int jn = 0; jn < NV; ++jn) {
       const int col = (warp * NV + jn) * 8 + 2 * c;
       if (col >= R) continue;
-      if (num_splits == 1) {
+      if (num_splits == 1 && !parts_always) {
         *reinterpret_cast<unsigned*>(out + ((size_t)b * H + head) * R + col) = pack_bf16(o[jn][2 * h] * inv, o[jn][2 * h + 1] * inv);
       } else {
         *reinterpret_cast<float2*>(part_o + prow * R + col) = make_float2(o[jn][2 * h], o[jn][2 * h + 1]);
       }
     }
-    if (num_splits > 1 && warp == 0 && c == 0)
+    if ((num_splits > 1 || parts_always) && warp == 0 && c == 0)
       *reinterpret_cast<float2*>(part_ml + prow * 2) = make_float2(m_run[h] * 0.6931471805599453f, l_run[h]);
   }
 }
@@ -259,7 +260,7 @@ int launch(const void* q, const void* cache, void* out, float* part_o, float* pa
   dim3 grid(n_seqs, (H + DL_HEADS - 1) / DL_HEADS, num_splits);
   return zk_launch_dependent(kern, grid, dim3(DL_THREADS), smem, stream, (const bf16*)q, (const bf16*)cache, (bf16*)out,
                              part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H, W, R, page_size, scale,
-                             num_splits, split_keys);
+                             num_splits, split_keys, (part_o && part_ml) ? 1 : 0);
 }
 
 }  // namespace
@@ -274,7 +275,9 @@ int zk_attn_decode_latent_takes(int H, int W, int R, int page_size) {
 }
 
 // q [n_seqs, H * W] bfloat16 (row b = sequence b); cache [pages, 1, page_size, W]; out [n_seqs, H * R]; partials as
-// for zk_attn_fwd when num_splits > 1 (rows ordered (split, sequence, head), R values each).
+// for zk_attn_fwd when num_splits > 1 (rows ordered (split, sequence, head), R values each).  With partials given and
+// num_splits = 1 the unnormalised sums go there all the same and `out` is not written: the caller's merge then
+// normalises them, for instance with a sink as one more term of the denominator.
 int zk_attn_decode_latent(const void* q, const void* cache, void* out, float* part_o, float* part_ml, const int* seq_start,
                           const int* seq_slot, const int* page_table, int pt_stride, int n_seqs, int H, int W, int R,
                           int page_size, float scale, int num_splits, int split_keys, cudaStream_t stream) {

@@ -72,7 +72,9 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
                           const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
                           const int* __restrict__ page_table, int pt_stride, int n_seqs, int H, int Hkv, int page_size,
                           int window, float scale, int num_splits, int split_keys, const float* __restrict__ bias_r1,
-                          const float* __restrict__ bias_r2, int cross, int keep, const float* __restrict__ sink) {
+                          const float* __restrict__ bias_r2, int cross, int keep, const float* __restrict__ sink,
+                          float softcap) {
+  // softcap > 0: a scaled score s becomes softcap * tanh(s / softcap) (then carried to base 2 like every score).
   // keep: with a window, the first `keep` keys of a sequence stay visible; the block whose chunk starts at the
   // window's lower edge also walks the tiles that hold them, before its own.
   // sink [H]: exp(sink_h) is one more term of head h's softmax denominator (no key, no value, unscaled); it enters
@@ -236,6 +238,7 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
       for (int i = 0; i < 4; ++i) {
         const int kp = kb + 8 * j + 2 * c + (i & 1);
         float sc = s[j][i] * scale2;
+        if (softcap > 0.f) sc = softcap * tanhf(s[j][i] * scale / softcap) * 1.4426950408889634f;
         if (biased) sc -= r1_2[i >> 1] * log1pf(r2[i >> 1] * (float)max(L - 1 - kp, 0));
         if (edge_tile) {
           const bool vis = (kp >= c0 || kp < keep_here) && kp < c1;
@@ -352,7 +355,7 @@ template <int HD, int NST>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_ml,
            const int* seq_start, const int* seq_slot, const int* page_table, int pt_stride, int n_seqs, int H, int Hkv,
            int page_size, int window, float scale, int num_splits, int split_keys, const float* r1, const float* r2,
-           int cross, int keep, const float* sink, cudaStream_t stream) {
+           int cross, int keep, const float* sink, float softcap, cudaStream_t stream) {
   auto kern = attn_decode_tc_kernel<HD, NST>;
   const size_t smem = 2 * NST * (size_t)DT_TK * HD * 2;
   static_assert(2 * NST * DT_TK * HD * 2 >= (2 * DT_WARPS * 16 + DT_WARPS * 16 * HD) * 4, "the merge fits in the tile buffers");
@@ -363,7 +366,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
   dim3 grid(n_seqs, Hkv * (cross ? Hkv : 1), num_splits);
   return zk_launch_dependent(kern, grid, dim3(DT_WARPS * 32), smem, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out,
                                               part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H, Hkv,
-                                              page_size, window, scale, num_splits, split_keys, r1, r2, cross, keep, sink);
+                                              page_size, window, scale, num_splits, split_keys, r1, r2, cross, keep, sink, softcap);
   return ZK_LAUNCH_STATUS();
 }
 
@@ -385,7 +388,7 @@ int zk_attn_decode_tc_takes(int H, int Hkv, int hd, int page_size) {
 int zk_attn_decode_tc(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_ml,
                       const int* seq_start, const int* seq_slot, const int* page_table, int pt_stride, int n_seqs, int H,
                       int Hkv, int hd, int page_size, int window, float scale, int num_splits, int split_keys,
-                      const float* bias_r1, const float* bias_r2, int cross, int keep, const float* sink,
+                      const float* bias_r1, const float* bias_r2, int cross, int keep, const float* sink, float softcap,
                       cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (keep < 0 || (keep > 0 && window <= 0) || (cross && (keep > 0 || sink))) return ZK_EINVAL;
@@ -402,12 +405,12 @@ int zk_attn_decode_tc(const void* q, const void* k_cache, const void* v_cache, v
   const bool short_chunks = num_splits > 1 && split_keys <= 4 * DT_TK;
   if (hd == 64 && short_chunks)
     return launch<64, 4>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
-                         Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, cross, keep, sink, stream);
+                         Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, cross, keep, sink, softcap, stream);
   if (hd == 64)
     return launch<64, 2>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
-                         Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, cross, keep, sink, stream);
+                         Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, cross, keep, sink, softcap, stream);
   return launch<128, 2>(q, k_cache, v_cache, out, part_o, part_ml, seq_start, seq_slot, page_table, pt_stride, n_seqs, H,
-                     Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, cross, keep, sink, stream);
+                     Hkv, page_size, window, scale, num_splits, split_keys, bias_r1, bias_r2, cross, keep, sink, softcap, stream);
 }
 
 }  // extern "C"

@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
                         const int* __restrict__ seq_slot, const int* __restrict__ page_table, int pt_stride, int H,
                         int Hkv, int page_size, int window, float scale, const float* __restrict__ bias_r1,
                         const float* __restrict__ bias_r2, float* __restrict__ part_o, float* __restrict__ part_ml,
-                        int keep, const float* __restrict__ sink) {
+                        int keep, const float* __restrict__ sink, float softcap) {
   // keep: with a window, the first `keep` positions of a sequence stay visible to every later query; the tiles
   // that hold them and lie below the window's reach are walked before the window's.
   // sink [H]: exp(sink_h) is one more term of head h's softmax denominator (no key, no value, unscaled).
@@ -213,6 +213,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
         const int kp = kb + 8 * j + 2 * c + (i & 1);
         const bool vis = row_ok[h] && (kp >= row_lo[h] || kp < keep) && kp < row_hi[h];
         float sc = s[j][i] * scale;
+        if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);     // capped scores
         if (biased && vis) sc -= r1[h] * log1pf(r2[h] * (float)(row_hi[h] - 1 - kp));
         s[j][i] = vis ? sc : -INFINITY;
         m_new[h] = fmaxf(m_new[h], s[j][i]);
@@ -299,7 +300,7 @@ template <int HD, int HDV, int GP>
 int launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq, const int* tile_q0,
            const int* cu_q, const int* seq_start, const int* seq_slot, const int* page_table, int pt_stride, int n_tiles,
            int H, int Hkv, int page_size, int window, float scale, const float* r1, const float* r2, float* part_o,
-           float* part_ml, int keep, const float* sink, cudaStream_t stream) {
+           float* part_ml, int keep, const float* sink, float softcap, cudaStream_t stream) {
   auto kern = attn_prefill_kernel<HD, HDV, GP>;
   const size_t smem = 2 * (size_t)PF_TK * (HD + HDV) * 2;
   if (smem > 48 * 1024) {
@@ -309,7 +310,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, c
   dim3 grid(n_tiles, Hkv * ((H / Hkv) / GP), part_o ? Hkv : 1);
   kern<<<grid, PF_WARPS * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out,
                                               tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table, pt_stride, H,
-                                              Hkv, page_size, window, scale, r1, r2, part_o, part_ml, keep, sink);
+                                              Hkv, page_size, window, scale, r1, r2, part_o, part_ml, keep, sink, softcap);
   return ZK_LAUNCH_STATUS();
 }
 
@@ -339,7 +340,7 @@ int zk_attn_prefill(const void* q, const void* k_cache, const void* v_cache, voi
                     const int* tile_q0, const int* cu_q, const int* seq_start, const int* seq_slot,
                     const int* page_table, int pt_stride, int n_tiles, int H, int Hkv, int hd, int vd,
                     int page_size, int window, float scale, const float* bias_r1, const float* bias_r2, float* part_o, float* part_ml,
-                    int keep, const float* sink, cudaStream_t stream) {
+                    int keep, const float* sink, float softcap, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (!zk_attn_prefill_takes(H, Hkv, hd, page_size) || ((bias_r1 == nullptr) != (bias_r2 == nullptr))) return ZK_EINVAL;
   if ((part_o == nullptr) != (part_ml == nullptr) || (part_o && Hkv > 65535)) return ZK_EINVAL;
@@ -350,14 +351,14 @@ int zk_attn_prefill(const void* q, const void* k_cache, const void* v_cache, voi
   if (hd == HDK && vd == HDK && gp == GPV)                                                                       \
     return launch<HDK, HDK, GPV>(q, k_cache, v_cache, out, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table,  \
                             pt_stride, n_tiles, H, Hkv, page_size, window, scale, bias_r1, bias_r2, part_o, part_ml,  \
-                            keep, sink, stream);
+                            keep, sink, softcap, stream);
   ZK_PF(64, 1) ZK_PF(64, 2) ZK_PF(64, 4) ZK_PF(64, 8)
   ZK_PF(128, 1) ZK_PF(128, 2) ZK_PF(128, 4) ZK_PF(128, 8)
 #undef ZK_PF
   if (hd == 128 && vd == 64 && gp == 1)      // narrow values: attention whose heads each have keys and values of their own
     return launch<128, 64, 1>(q, k_cache, v_cache, out, tile_seq, tile_q0, cu_q, seq_start, seq_slot, page_table,
                               pt_stride, n_tiles, H, Hkv, page_size, window, scale, bias_r1, bias_r2, part_o, part_ml,
-                              keep, sink, stream);
+                              keep, sink, softcap, stream);
   return ZK_EINVAL;
 }
 

@@ -181,11 +181,11 @@ __global__ void fill_normal_kernel(T* __restrict__ out, size_t n, unsigned long 
   }
 }
 
-// x[r, :] += (m[r, :] * rsqrt(mean(m^2) + eps)) * w: the RMSNorm of a sublayer's OUTPUT added to
-// the residual rows, all in float32.  One block per row; the row of m stays in registers when it
+// x[r, :] += out_scale * ((m[r, :] * rsqrt(mean(m^2) + eps)) * w): the RMSNorm of a sublayer's OUTPUT added to
+// the residual rows (out_scale 1), or a share of it (two mixers side by side add half each), all in float32.  One block per row; the row of m stays in registers when it
 // fits (16 values per thread), else it is read twice.
 __global__ void rmsnorm_add_kernel(const float* __restrict__ m, const float* __restrict__ w, float* __restrict__ x,
-                                   int dim, float eps) {
+                                   int dim, float eps, float out_scale) {
   __shared__ float scratch[32];
   zk_let_next_start();
   zk_wait_prior();
@@ -211,16 +211,16 @@ __global__ void rmsnorm_add_kernel(const float* __restrict__ m, const float* __r
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const int d = threadIdx.x + i * blockDim.x;
-      if (d < dim) xr[d] += (keep[i] * scale) * w[d];
+      if (d < dim) xr[d] += out_scale * ((keep[i] * scale) * w[d]);
     }
   } else {
-    for (int d = threadIdx.x; d < dim; d += blockDim.x) xr[d] += (mr[d] * scale) * w[d];
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) xr[d] += out_scale * ((mr[d] * scale) * w[d]);
   }
 }
 
 // The same with 16-byte loads and stores (dim a multiple of 4, at most 16 values per thread, aligned rows).
 __global__ void rmsnorm_add_vec4_kernel(const float* __restrict__ m, const float* __restrict__ w, float* __restrict__ x,
-                                        int dim, float eps) {
+                                        int dim, float eps, float out_scale) {
   __shared__ float scratch[32];
   zk_let_next_start();
   zk_wait_prior();
@@ -250,8 +250,125 @@ __global__ void rmsnorm_add_vec4_kernel(const float* __restrict__ m, const float
     const int d = threadIdx.x + i * blockDim.x;
     if (d >= n4) continue;
     const float4 wv = reinterpret_cast<const float4*>(w)[d];
-    xr[d] = make_float4(xv[i].x + (v[i].x * scale) * wv.x, xv[i].y + (v[i].y * scale) * wv.y,
-                        xv[i].z + (v[i].z * scale) * wv.z, xv[i].w + (v[i].w * scale) * wv.w);
+    xr[d] = make_float4(xv[i].x + out_scale * ((v[i].x * scale) * wv.x), xv[i].y + out_scale * ((v[i].y * scale) * wv.y),
+                        xv[i].z + out_scale * ((v[i].z * scale) * wv.z), xv[i].w + out_scale * ((v[i].w * scale) * wv.w));
+  }
+}
+
+// Layer norm: y[r, :] = (x[src(r), :] - mean) / sqrt(var + eps) * w + b, var the mean of the squared deviations
+// (two passes over the row, which stays in registers when it fits: 16 values per thread), float32 arithmetic.
+// src(r) = rows ? rows[r] : r.  One block per output row; b may be null (no bias).
+template <typename TO>
+__global__ void layernorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+                                 const float* __restrict__ b, TO* __restrict__ y, int dim, float eps) {
+  __shared__ float scratch[32];
+  zk_let_next_start();
+  zk_wait_prior();
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * dim;
+  TO* yr = y + (size_t)r * dim;
+  float keep[16];
+  const bool fits = dim <= 16 * (int)blockDim.x;
+  float sum = 0.f;
+  if (fits) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int d = threadIdx.x + i * blockDim.x;
+      keep[i] = d < dim ? xr[d] : 0.f;
+      sum += keep[i];
+    }
+  } else {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) sum += xr[d];
+  }
+  const float mean = block_sum(sum, scratch) / (float)dim;
+  float ss = 0.f;
+  if (fits) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int d = threadIdx.x + i * blockDim.x;
+      const float c = d < dim ? keep[i] - mean : 0.f;
+      ss = fmaf(c, c, ss);
+    }
+  } else {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+      const float c = xr[d] - mean;
+      ss = fmaf(c, c, ss);
+    }
+  }
+  const float scale = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dim + eps);
+  if (fits) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int d = threadIdx.x + i * blockDim.x;
+      if (d < dim) yr[d] = from_f32<TO>(((keep[i] - mean) * scale) * w[d] + (b ? b[d] : 0.f));
+    }
+  } else {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x)
+      yr[d] = from_f32<TO>(((xr[d] - mean) * scale) * w[d] + (b ? b[d] : 0.f));
+  }
+}
+
+// A gate per value: rows[t, h, j] *= sigmoid(gate[t * ld_gate + h * valid + j]) for j < valid, in place; a head's row is
+// `width` values of which the first `valid` are gated (the rest is padding and left alone).  gate float32.
+template <typename T>
+__global__ void value_gate_kernel(T* __restrict__ rows, const float* __restrict__ gate, int ld_gate, int n, int H, int width,
+                                  int valid) {
+  zk_let_next_start();
+  zk_wait_prior();
+  const size_t total = (size_t)n * H * valid;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t th = i / valid, t = th / H;
+    const int j = (int)(i - th * valid), hh = (int)(th - t * H);
+    const float g = gate[t * ld_gate + (size_t)hh * valid + j];
+    T* v = rows + th * width + j;
+    *v = from_f32<T>(to_f32(*v) / (1.0f + expf(-g)));
+  }
+}
+
+// The same for bfloat16 rows in 16-byte pieces (width and valid multiples of 8, gate rows 16-byte aligned).
+__global__ void value_gate_vec8_kernel(uint4* __restrict__ rows, const float* __restrict__ gate, int ld_gate, int pieces, int H,
+                                       int per_head, int valid_pieces) {
+  zk_let_next_start();
+  zk_wait_prior();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= pieces) return;
+  const int th = i / valid_pieces, j = i - th * valid_pieces, t = th / H, hh = th - t * H;
+  const float4* g4 = reinterpret_cast<const float4*>(gate + (size_t)t * ld_gate + ((size_t)hh * valid_pieces + j) * 8);
+  const float4 ga = g4[0], gb = g4[1];
+  const float g[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+  uint4* dst = rows + (size_t)th * per_head + j;
+  uint4 v = *dst;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 f = __bfloat1622float2(p[k]);
+    p[k] = __floats2bfloat162_rn(f.x / (1.0f + expf(-g[2 * k])), f.y / (1.0f + expf(-g[2 * k + 1])));
+  }
+  *dst = v;
+}
+
+// Heads divided by their root mean square and gated: y[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) *
+// silu(gate[t * ld_gate + h * e + :]).  o and gate float32 (o rows packed, H * e wide), y in the run dtype.
+// One warp per (token, head); the sum of squares is added in lane order then over the warp's tree.
+template <typename TO>
+__global__ void unit_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate, int ld_gate,
+                                      TO* __restrict__ y, long long items, int H, int e, float eps) {
+  zk_let_next_start();
+  zk_wait_prior();
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= items) return;
+  const long long t = item / H;
+  const int h = (int)(item - t * H);
+  const float* src = o + (size_t)item * e;
+  const float* g = gate + (size_t)t * ld_gate + (size_t)h * e;
+  float ss = 0.f;
+  for (int j = lane; j < e; j += 32) ss = fmaf(src[j], src[j], ss);
+  ss = warp_sum(ss);
+  const float scale = 1.0f / sqrtf(ss / (float)e + eps);
+  for (int j = lane; j < e; j += 32) {
+    const float z = g[j];
+    y[(size_t)item * e + j] = from_f32<TO>((src[j] * scale) * (z / (1.0f + expf(-z))));
   }
 }
 
@@ -562,6 +679,13 @@ __global__ void gate_add_kernel(const float* __restrict__ x, const float* __rest
   for (int d = threadIdx.x; d < out_dim; d += blockDim.x) mr[d] = fmaf(gate, sr[d], mr[d]);
 }
 
+// x *= scale, in place (float32): logits that a design multiplies by a constant.
+__global__ void scale_kernel(float* __restrict__ x, size_t total, float scale) {
+  zk_let_next_start();
+  zk_wait_prior();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) x[i] *= scale;
+}
+
 extern "C" {
 
 int zk_fill_normal(void* out, long long n, long long seed, float mean, float std, int dtype, cudaStream_t stream) {
@@ -642,7 +766,8 @@ static inline int grid_for_total(size_t total, int threads) {
   return (int)(want < 148 * 16 ? want : 148 * 16);
 }
 
-int zk_rmsnorm_add(const float* m, const float* w, float* x, int n, int dim, float eps, cudaStream_t stream) {
+int zk_rmsnorm_add(const float* m, const float* w, float* x, int n, int dim, float eps, float out_scale,
+                   cudaStream_t stream) {
   if (n <= 0) return 0;
   if (dim <= 0) return ZK_EINVAL;
   int threads = 32;
@@ -650,9 +775,9 @@ int zk_rmsnorm_add(const float* m, const float* w, float* x, int n, int dim, flo
   const bool aligned = (reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) % 16 == 0;
   if (dim % 4 == 0 && dim <= 16 * threads && aligned) {
     while (threads > 32 && threads * 4 >= 2 * dim) threads >>= 1;   // no idle warps for short rows
-    return zk_launch_dependent(rmsnorm_add_vec4_kernel, dim3(n), dim3(threads), 0, stream, m, w, x, dim, eps);
+    return zk_launch_dependent(rmsnorm_add_vec4_kernel, dim3(n), dim3(threads), 0, stream, m, w, x, dim, eps, out_scale);
   }
-  return zk_launch_dependent(rmsnorm_add_kernel, dim3(n), dim3(threads), 0, stream, m, w, x, dim, eps);
+  return zk_launch_dependent(rmsnorm_add_kernel, dim3(n), dim3(threads), 0, stream, m, w, x, dim, eps, out_scale);
 }
 
 int zk_activation(const void* in, void* out, long long total, int kind, int dtype, cudaStream_t stream) {
@@ -681,6 +806,12 @@ int zk_softcap(float* x, long long total, float cap, cudaStream_t stream) {
   if (!(cap > 0.f)) return ZK_EINVAL;
   const int threads = 256, blocks = grid_for_total((size_t)total, threads);
   return zk_launch_dependent(softcap_kernel, dim3(blocks), dim3(threads), 0, stream, x, (size_t)total, cap);
+}
+
+int zk_scale(float* x, long long total, float scale, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  const int threads = 256, blocks = grid_for_total((size_t)total, threads);
+  return zk_launch_dependent(scale_kernel, dim3(blocks), dim3(threads), 0, stream, x, (size_t)total, scale);
 }
 
 int zk_weighted_sum(const float* planes, const float* w, int n_terms, long long plane, float* out, cudaStream_t stream) {
@@ -761,6 +892,54 @@ int zk_head_gate(void* rows, const float* gate, int ld_gate, int n, int H, int w
     return zk_launch_dependent(head_gate_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)rows, gate, ld_gate, n, H, width);
   if (dtype == ZK_BF16)
     return zk_launch_dependent(head_gate_kernel<bf16>, dim3(blocks), dim3(threads), 0, stream, (bf16*)rows, gate, ld_gate, n, H, width);
+  return ZK_EINVAL;
+}
+
+// Layer norm of float32 rows (all, or those listed in `rows`) with weight and optional bias into `out_dtype`.
+int zk_layernorm(const float* x, const int* rows, const float* w, const float* b, void* y, int n_out, int dim, float eps,
+                 int out_dtype, cudaStream_t stream) {
+  if (n_out <= 0) return 0;
+  if (dim <= 0 || !w) return ZK_EINVAL;
+  int threads = 32;
+  while (threads < 256 && threads * 4 < dim) threads <<= 1;
+  if (out_dtype == ZK_F32)
+    return zk_launch_dependent(layernorm_kernel<float>, dim3(n_out), dim3(threads), 0, stream, x, rows, w, b, (float*)y, dim, eps);
+  if (out_dtype == ZK_BF16)
+    return zk_launch_dependent(layernorm_kernel<bf16>, dim3(n_out), dim3(threads), 0, stream, x, rows, w, b, (bf16*)y, dim, eps);
+  return ZK_EINVAL;
+}
+
+// rows [n, H * width] (run dtype) gated value by value: gate float32, rows `ld_gate` apart, H * valid logits a row.
+int zk_value_gate(void* rows, const float* gate, int ld_gate, int n, int H, int width, int valid, int dtype,
+                  cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (H <= 0 || width <= 0 || valid <= 0 || valid > width || ld_gate < H * valid) return ZK_EINVAL;
+  if (dtype == ZK_BF16 && width % 8 == 0 && valid % 8 == 0 && ld_gate % 4 == 0 && (uintptr_t)rows % 16 == 0 &&
+      (uintptr_t)gate % 16 == 0 && (size_t)n * H * (valid / 8) < 0x7fffffffULL) {
+    const int pieces = n * H * (valid / 8);
+    return zk_launch_dependent(value_gate_vec8_kernel, dim3((pieces + 255) / 256), dim3(256), 0, stream, (uint4*)rows, gate,
+                               ld_gate, pieces, H, width / 8, valid / 8);
+  }
+  const int threads = 256, blocks = grid_for_total((size_t)n * H * valid, threads);
+  if (dtype == ZK_F32)
+    return zk_launch_dependent(value_gate_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)rows, gate, ld_gate, n, H, width, valid);
+  if (dtype == ZK_BF16)
+    return zk_launch_dependent(value_gate_kernel<bf16>, dim3(blocks), dim3(threads), 0, stream, (bf16*)rows, gate, ld_gate, n, H, width, valid);
+  return ZK_EINVAL;
+}
+
+// y [n, H * e] (out_dtype) = every head of o [n, H * e] (float32) over its root mean square, times silu(gate).
+int zk_unit_norm_gate(const float* o, const float* gate, int ld_gate, void* y, int n, int H, int e, float eps, int out_dtype,
+                      cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (H <= 0 || e <= 0 || ld_gate < H * e) return ZK_EINVAL;
+  const long long items = (long long)n * H;
+  const int warps = 4;
+  const int blocks = (int)((items + warps - 1) / warps);
+  if (out_dtype == ZK_F32)
+    return zk_launch_dependent(unit_norm_gate_kernel<float>, dim3(blocks), dim3(warps * 32), 0, stream, o, gate, ld_gate, (float*)y, items, H, e, eps);
+  if (out_dtype == ZK_BF16)
+    return zk_launch_dependent(unit_norm_gate_kernel<bf16>, dim3(blocks), dim3(warps * 32), 0, stream, o, gate, ld_gate, (bf16*)y, items, H, e, eps);
   return ZK_EINVAL;
 }
 

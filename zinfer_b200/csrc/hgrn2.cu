@@ -16,6 +16,9 @@
 // warp w sums those of tokens w and w + 8 in the order of the warps.  q and f of the next sixteen tokens are fetched into
 // registers while the current sixteen are worked on, and go into the other half of a double buffer.  The order of every sum is fixed by the layout alone, so a
 // sequence cut into steps gives the same bits as the whole.
+//
+// The same kernel runs the recurrence of a retention layer (its KEYED form): a key projection in place of the gate and
+// one fixed decay per head, S_t = decay_h S_{t-1} + k_t v_t^T; retention_prepare_kernel rotates q and k and scales k first.
 #include "common.cuh"
 #include <math.h>
 
@@ -38,12 +41,43 @@ __global__ void hgrn2_gates_kernel(float* __restrict__ qfv, int ld, const float*
   }
 }
 
-// DPT: channels per warp; TT: tokens staged at once (sixteen, or eight or four where more do not fit shared memory)
-template <int DPT, int TT>
+// What a retention layer does to its projections before the recurrence, in place on the float32 rows [q (H*d) | k (H*d)
+// | ...]: the first n_rot entries of every q and k head are rotated by the token's position (entry i pairs with entry
+// i + n_rot/2, angle = float(pos) * inv_freq[i]; inv_freq null = no rotation), then k is multiplied by key_scale.
+__global__ void retention_prepare_kernel(float* __restrict__ qk, int ld, const float* __restrict__ inv_freq, int n_rot,
+                                         float key_scale, const int* __restrict__ tok_pos, int n, int H, int d) {
+  zk_let_next_start();
+  zk_wait_prior();
+  const int half = inv_freq ? n_rot >> 1 : 0;
+  const int per_head = d - half;                      // work items of a head: its pairs, then its unrotated entries
+  const size_t total = (size_t)n * 2 * H * per_head;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t th = idx / per_head;
+    const int i = (int)(idx - th * per_head);
+    const size_t t = th / (2 * H);
+    const int s = (int)(th - t * 2 * H);              // head slot: the H query heads, then the H key heads
+    float* head = qk + t * ld + (size_t)s * d;
+    const float mul = s >= H ? key_scale : 1.0f;
+    if (i < half) {
+      const float ang = (float)tok_pos[t] * inv_freq[i];
+      const float c = cosf(ang), sn = sinf(ang);
+      const float u = head[i], v = head[i + half];
+      head[i] = (u * c - v * sn) * mul;
+      head[i + half] = (v * c + u * sn) * mul;
+    } else if (s >= H) {
+      head[i + half] *= mul;
+    }
+  }
+}
+
+// DPT: channels per warp; TT: tokens staged at once (sixteen, or eight or four where more do not fit shared memory).
+// KEYED: the recurrence of a retention layer instead, S_t = decay_h S_{t-1} + k_t v_t^T with one fixed decay per head
+// (`decay` [H]); the row's second part then holds the keys k_t in place of the gates.
+template <int DPT, int TT, bool KEYED>
 __global__ void __launch_bounds__(HG_R * 32)
     hgrn2_scan_kernel(const float* __restrict__ qfv, int ld, float* __restrict__ state, long long state_stride,
                       float* __restrict__ o, const int* __restrict__ cu_q, const int* __restrict__ seq_slot, int H, int d,
-                      int e) {
+                      int e, const float* __restrict__ decay) {
   constexpr int DM = HG_R * DPT;                                     // channels the block covers, >= d
   constexpr int NL = (TT * DM + HG_R * 32 - 1) / (HG_R * 32);     // q (and f) values a thread fetches per group of tokens
   __shared__ __align__(16) float qs[2][TT][DM];
@@ -64,6 +98,7 @@ __global__ void __launch_bounds__(HG_R * 32)
   }
   zk_wait_prior();   // qfv is the kernel before's result
   const int t0 = cu_q[b], t1 = cu_q[b + 1];
+  const float dk = KEYED ? decay[h] : 0.f;
   float* st = state + (size_t)seq_slot[b] * state_stride + (size_t)h * d * e;
   float S[DPT];
 #pragma unroll
@@ -127,7 +162,8 @@ __global__ void __launch_bounds__(HG_R * 32)
           const float ff[4] = {f4.x, f4.y, f4.z, f4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            S[k4 + j] = fmaf(ff[j], S[k4 + j], fmaf(-ff[j], v, v));     // f S + (1 - f) v
+            if (KEYED) S[k4 + j] = fmaf(dk, S[k4 + j], ff[j] * v);               // decay S + k v
+            else S[k4 + j] = fmaf(ff[j], S[k4 + j], fmaf(-ff[j], v, v));        // f S + (1 - f) v
             acc = fmaf(S[k4 + j], qq[j], acc);
           }
         }
@@ -135,7 +171,8 @@ __global__ void __launch_bounds__(HG_R * 32)
 #pragma unroll
         for (int k = 0; k < DPT; ++k) {
           const float f = fs[buf][tt][row0 + k];
-          S[k] = fmaf(f, S[k], fmaf(-f, v, v));
+          if (KEYED) S[k] = fmaf(dk, S[k], f * v);
+          else S[k] = fmaf(f, S[k], fmaf(-f, v, v));
           acc = fmaf(S[k], qs[buf][tt][row0 + k], acc);
         }
       }
@@ -194,8 +231,8 @@ int zk_hgrn2_scan(float* qfv, int ld, const float* f_bias, const float* lower, f
   }
   dim3 grid(n_seqs, H, (e + 31) / 32);
 #define ZK_HG(DP)                                                                                                    \
-  return zk_launch_dependent(hgrn2_scan_kernel<DP, (DP > 32 ? 4 : (DP > 16 ? 8 : 16))>, grid, dim3(HG_R * 32), 0, stream, (const float*)qfv, ld, \
-                             state, state_stride, o, cu_q, seq_slot, H, d, e)
+  return zk_launch_dependent(hgrn2_scan_kernel<DP, (DP > 32 ? 4 : (DP > 16 ? 8 : 16)), false>, grid, dim3(HG_R * 32), 0, stream, (const float*)qfv, ld, \
+                             state, state_stride, o, cu_q, seq_slot, H, d, e, (const float*)nullptr)
   const int dpt = (d + HG_R - 1) / HG_R;
   if (dpt <= 1) ZK_HG(1);
   if (dpt <= 2) ZK_HG(2);
@@ -205,6 +242,40 @@ int zk_hgrn2_scan(float* qfv, int ld, const float* f_bias, const float* lower, f
   if (dpt <= 32) ZK_HG(32);
   ZK_HG(64);
 #undef ZK_HG
+}
+
+// Retention: per head S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t.  qkv float32 [n, >= 2*H*d + H*e] with rows `ld`
+// floats apart, [q | k | v | ...] as the projections gave them; q and k are REPLACED by their rotated forms (k also
+// times key_scale).  decay float32 [H]; inv_freq float32 [n_rot / 2] or null; tok_pos [n]; state, o, cu_q, seq_slot as for
+// zk_hgrn2_scan.
+int zk_retention_scan(float* qkv, int ld, const float* decay, const float* inv_freq, int n_rot, float key_scale,
+                      const int* tok_pos, float* state, long long state_stride, float* o, const int* cu_q,
+                      const int* seq_slot, int n, int n_seqs, int H, int d, int e, cudaStream_t stream) {
+  if (n_seqs <= 0 || n <= 0) return 0;
+  if (H <= 0 || d <= 0 || e <= 0 || d > HG_MAX_D || ld < 2 * H * d + H * e || !decay || !tok_pos) return ZK_EINVAL;
+  if (inv_freq && (n_rot <= 0 || (n_rot & 1) || n_rot > d)) return ZK_EINVAL;
+  if (inv_freq || key_scale != 1.0f) {
+    const size_t total = (size_t)n * 2 * H * (d - (inv_freq ? n_rot / 2 : 0));
+    const int threads = 256;
+    const size_t want = (total + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    const int rc = zk_launch_dependent(retention_prepare_kernel, dim3(blocks), dim3(threads), 0, stream, qkv, ld, inv_freq, n_rot,
+                                       key_scale, tok_pos, n, H, d);
+    if (rc != 0) return rc;
+  }
+  dim3 grid(n_seqs, H, (e + 31) / 32);
+#define ZK_RT(DP)                                                                                                    \
+  return zk_launch_dependent(hgrn2_scan_kernel<DP, (DP > 32 ? 4 : (DP > 16 ? 8 : 16)), true>, grid, dim3(HG_R * 32), 0, stream, (const float*)qkv, ld, \
+                             state, state_stride, o, cu_q, seq_slot, H, d, e, decay)
+  const int dpt = (d + HG_R - 1) / HG_R;
+  if (dpt <= 1) ZK_RT(1);
+  if (dpt <= 2) ZK_RT(2);
+  if (dpt <= 4) ZK_RT(4);
+  if (dpt <= 8) ZK_RT(8);
+  if (dpt <= 16) ZK_RT(16);
+  if (dpt <= 32) ZK_RT(32);
+  ZK_RT(64);
+#undef ZK_RT
 }
 
 }  // extern "C"

@@ -76,11 +76,12 @@ __device__ __forceinline__ void rows_dot(const T* const (&w)[R], const float* __
 
 // With `tokens` null the experts are not looked up through a table: `table` is then [n, top], the experts a
 // router chose for each token.
+// Ids n_experts .. n_experts + n_ident - 1 name identity experts (no weights: the expert's output is its input).
 __device__ __forceinline__ int moe_expert(const int* __restrict__ tokens, const int* __restrict__ table, int t, int k,
-                                          int top, int vocab, int n_experts, int* status) {
+                                          int top, int vocab, int n_experts, int* status, int n_ident = 0) {
   if (!tokens) {
     int e = table[(size_t)t * top + k];
-    if (e < 0 || e >= n_experts) {
+    if (e < 0 || e >= n_experts + n_ident) {
       if (threadIdx.x == 0) atomicExch(status, 4);
       e = 0;
     }
@@ -100,13 +101,14 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
     moe_gate_up_kernel(const T* __restrict__ x, const int* __restrict__ tokens, const int* __restrict__ table,
                        const T* __restrict__ w_gu, int il, T* __restrict__ h, int D, int F,
-                       int top, int vocab, int n_experts, int units_per_block, int* status) {
+                       int top, int vocab, int n_experts, int units_per_block, int* status, int n_ident) {
   extern __shared__ float xs[];     // [D]
   zk_let_next_start();
   zk_wait_prior();
   const int t = blockIdx.x / top, k = blockIdx.x % top;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int e = moe_expert(tokens, table, t, k, top, vocab, n_experts, status);
+  const int e = moe_expert(tokens, table, t, k, top, vocab, n_experts, status, n_ident);
+  if (e >= n_experts) return;       // an identity expert has no hidden units
   for (int d = threadIdx.x; d < D; d += blockDim.x) xs[d] = to_f32(x[(size_t)t * D + d]);
   __syncthreads();
   const T* w = w_gu + (size_t)e * 2 * F * D;
@@ -140,8 +142,10 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
     moe_down_kernel(const T* __restrict__ h, const int* __restrict__ tokens, const int* __restrict__ table,
                     const T* __restrict__ w_down, float* __restrict__ y, int D, int F, int top, int vocab,
-                    int n_experts, int outs_per_block, int accumulate, int* status, const float* __restrict__ route_w) {
-  // route_w [n, top]: the weight of each of the token's experts (null: 1/top each)
+                    int n_experts, int outs_per_block, int accumulate, int* status, const float* __restrict__ route_w,
+                    int n_ident, const T* __restrict__ x) {
+  // route_w [n, top]: the weight of each of the token's experts (null: 1/top each).  x [n, D]: the rows the experts
+  // read, which an identity expert (n_ident > 0) hands on as they are.
   extern __shared__ float hs[];     // [top][F]
   zk_let_next_start();
   zk_wait_prior();
@@ -156,7 +160,13 @@ __global__ void __launch_bounds__(MOE_WARPS * 32)
 #pragma unroll
     for (int u = 0; u < MOE_UNITS; ++u) acc[u] = 0.f;
     for (int k = 0; k < top; ++k) {
-      const int e = moe_expert(tokens, table, t, k, top, vocab, n_experts, status);
+      const int e = moe_expert(tokens, table, t, k, top, vocab, n_experts, status, n_ident);
+      if (e >= n_experts) {          // identity: the weight times the input row
+        const float wi = route_w ? route_w[(size_t)t * top + k] : weight;
+#pragma unroll
+        for (int u = 0; u < MOE_UNITS; ++u) acc[u] += wi * to_f32(x[(size_t)t * D + min(db + u, d1 - 1)]);
+        continue;
+      }
       const T* rows[MOE_UNITS];
 #pragma unroll
       for (int u = 0; u < MOE_UNITS; ++u) rows[u] = w_down + ((size_t)e * D + min(db + u, d1 - 1)) * F;
@@ -203,7 +213,7 @@ __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict
 // tile per expert.  One block; the order of an expert's rows is not fixed, which no row's result depends on.
 __global__ void __launch_bounds__(1024)
     moe_expert_rows_kernel(const int* __restrict__ ids, int P, int E, int top, int tile, int cap,
-                           int* __restrict__ row_token, int* __restrict__ pair_row, int* __restrict__ tile_group) {
+                           int* __restrict__ row_token, int* __restrict__ pair_row, int* __restrict__ tile_group, int n_ident) {
   extern __shared__ int sh[];      // count [E], start [E]
   int* count = sh;
   int* start = sh + E;
@@ -213,7 +223,9 @@ __global__ void __launch_bounds__(1024)
   for (int e = tid; e < E; e += nt) count[e] = 0;
   for (int i = tid; i < cap; i += nt) row_token[i] = -1;
   __syncthreads();
-  for (int i = tid; i < P; i += nt) atomicAdd(&count[min(max(ids[i], 0), E - 1)], 1);
+  // a pair whose id names an identity expert (E .. E + n_ident - 1) gets no row: pair_row = -1
+  for (int i = tid; i < P; i += nt)
+    if (!(n_ident > 0 && ids[i] >= E)) atomicAdd(&count[min(max(ids[i], 0), E - 1)], 1);
   __syncthreads();
   if (tid == 0) {
     int run = 0;
@@ -228,6 +240,10 @@ __global__ void __launch_bounds__(1024)
   }
   __syncthreads();
   for (int i = tid; i < P; i += nt) {
+    if (n_ident > 0 && ids[i] >= E) {
+      pair_row[i] = -1;
+      continue;
+    }
     const int e = min(max(ids[i], 0), E - 1);
     const int r = start[e] + atomicAdd(&count[e], 1);
     row_token[r] = i / top;
@@ -235,16 +251,25 @@ __global__ void __launch_bounds__(1024)
   }
 }
 
+// A pair without a row (pair_row < 0) stands for an identity expert: its term is the weight times the token's own input
+// row x[t] (run dtype: float32 or, with x_bf16, bfloat16).
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_row, float* __restrict__ out,
-                                   int D, int top, int accumulate, const float* __restrict__ route_w) {
+                                   int D, int top, int accumulate, const float* __restrict__ route_w,
+                                   const void* __restrict__ x, int x_bf16) {
   zk_let_next_start();
   zk_wait_prior();
   const int t = blockIdx.x;
   const float weight = 1.0f / (float)top;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float acc = 0.f;
-    for (int k = 0; k < top; ++k)
-      acc += (route_w ? route_w[(size_t)t * top + k] : weight) * y[(size_t)pair_row[t * top + k] * D + d];
+    for (int k = 0; k < top; ++k) {
+      const int r = pair_row[t * top + k];
+      float term;
+      if (r >= 0) term = y[(size_t)r * D + d];
+      else if (!x) term = 0.f;
+      else term = x_bf16 ? to_f32(reinterpret_cast<const bf16*>(x)[(size_t)t * D + d]) : reinterpret_cast<const float*>(x)[(size_t)t * D + d];
+      acc += (route_w ? route_w[(size_t)t * top + k] : weight) * term;
+    }
     out[(size_t)t * D + d] = accumulate ? out[(size_t)t * D + d] + acc : acc;
   }
 }
@@ -256,10 +281,12 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
     moe_router_kernel(const T* __restrict__ x, const float* __restrict__ w, int* __restrict__ ids, float* __restrict__ wts,
-                      int D, int E, int top) {
-  extern __shared__ float rs[];     // [D] the token's row, [E] logits then scores
+                      int D, int E, int top, const float* __restrict__ correction) {
+  // correction [E] (or null): the experts are CHOSEN by score + correction; the weights use the scores alone.
+  extern __shared__ float rs[];     // [D] the token's row, [E] logits then scores, [E] what the choice looks at
   float* xs = rs;
   float* z = rs + D;
+  float* pick = z + E;
   zk_let_next_start();
   zk_wait_prior();
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -297,13 +324,15 @@ __global__ void __launch_bounds__(MOE_WARPS * 32)
   }
   sum = warp_sum(sum);
   __syncwarp();
+  for (int e = lane; e < E; e += 32) pick[e] = correction ? z[e] / sum + correction[e] : z[e];
+  __syncwarp();
   float chosen_sum = 0.f;
   for (int k = 0; k < top; ++k) {
-    float best = -1.f;
+    float best = -INFINITY;
     int arg = E;
     for (int e = lane; e < E; e += 32)
-      if (z[e] > best) {          // ascending e within a lane: the lower index wins a tie
-        best = z[e];
+      if (pick[e] > best) {       // ascending e within a lane: the lower index wins a tie
+        best = pick[e];
         arg = e;
       }
 #pragma unroll
@@ -315,12 +344,15 @@ __global__ void __launch_bounds__(MOE_WARPS * 32)
         arg = oa;
       }
     }
+    arg = min(arg, E - 1);        // (only scores that are no numbers leave arg at E)
+    const float score = z[arg] / sum;
+    __syncwarp();
     if (lane == 0) {
       ids[(size_t)t * top + k] = arg;
-      wts[(size_t)t * top + k] = best / sum;
-      z[arg] = -2.f;              // taken
+      wts[(size_t)t * top + k] = score;
+      pick[arg] = -INFINITY;      // taken
     }
-    chosen_sum += best / sum;
+    chosen_sum += score;
     __syncwarp();
   }
   const float inv = 1.0f / (chosen_sum + 1e-20f);
@@ -333,7 +365,7 @@ namespace {
 template <typename T>
 int launch_moe(const void* x, const int* tokens, const int* table, const void* w_gu, int il,
                const void* w_down, void* h, float* y, int n, int D, int F, int top, int vocab, int n_experts,
-               int accumulate, int* status, const float* route_w, cudaStream_t stream) {
+               int accumulate, int* status, const float* route_w, int n_ident, cudaStream_t stream) {
   const int per = 16 / (int)sizeof(T);   // elements per 16 bytes
   auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   const bool vec_gu = D % 8 == 0 && D % per == 0 && aligned(w_gu);
@@ -358,7 +390,7 @@ int launch_moe(const void* x, const int* tokens, const int* table, const void* w
       if (e != cudaSuccess) return (int)e;                                                                            \
     }                                                                                                                 \
     rc = zk_launch_dependent(kern, grid_gu, dim3(MOE_WARPS * 32), smem_gu, stream, (const T*)x, tokens, table,        \
-                             (const T*)w_gu, il, (T*)h, D, F, top, vocab, n_experts, units, status);                  \
+                             (const T*)w_gu, il, (T*)h, D, F, top, vocab, n_experts, units, status, n_ident);         \
   } while (0)
 #define ZK_MOE_DN(V)                                                                                                  \
   do {                                                                                                                \
@@ -368,7 +400,8 @@ int launch_moe(const void* x, const int* tokens, const int* table, const void* w
       if (e != cudaSuccess) return (int)e;                                                                            \
     }                                                                                                                 \
     rc = zk_launch_dependent(kern, grid_dn, dim3(MOE_WARPS * 32), smem_dn, stream, (const T*)h, tokens, table,        \
-                             (const T*)w_down, y, D, F, top, vocab, n_experts, outs, accumulate, status, route_w);    \
+                             (const T*)w_down, y, D, F, top, vocab, n_experts, outs, accumulate, status, route_w,     \
+                             n_ident, (const T*)x);                                                                   \
   } while (0)
   if (vec_gu) ZK_MOE_GU(true); else ZK_MOE_GU(false);
   if (rc != 0) return rc;
@@ -390,33 +423,35 @@ int zk_moe_table(const void* x, const int* tokens, const int* table, const void*
   if (n <= 0) return 0;
   if (D <= 0 || F <= 0 || top <= 0 || vocab <= 0 || n_experts <= 0 || il < 0 || (il > 0 && F % il)) return ZK_EINVAL;
   if (dtype == ZK_F32)
-    return launch_moe<float>(x, tokens, table, w_gu, il, w_down, h, y, n, D, F, top, vocab, n_experts, accumulate, status, nullptr, stream);
+    return launch_moe<float>(x, tokens, table, w_gu, il, w_down, h, y, n, D, F, top, vocab, n_experts, accumulate, status, nullptr, 0, stream);
   if (dtype == ZK_BF16)
-    return launch_moe<bf16>(x, tokens, table, w_gu, il, w_down, h, y, n, D, F, top, vocab, n_experts, accumulate, status, nullptr, stream);
+    return launch_moe<bf16>(x, tokens, table, w_gu, il, w_down, h, y, n, D, F, top, vocab, n_experts, accumulate, status, nullptr, 0, stream);
   return ZK_EINVAL;
 }
 
 // The same with the experts a router chose: route_ids [n, top] int32 and route_w [n, top] float32 (the weight of
-// each), y_t = sum_k route_w[t, k] * Expert[route_ids[t, k]](x_t), added in the order of k.
+// each), y_t = sum_k route_w[t, k] * Expert[route_ids[t, k]](x_t), added in the order of k.  Ids n_experts ..
+// n_experts + n_ident - 1 are identity experts: Expert(x_t) = x_t.
 int zk_moe_routed(const void* x, const int* route_ids, const float* route_w, const void* w_gu, int il, const void* w_down,
                   void* h, float* y, int n, int D, int F, int top, int n_experts, int accumulate, int dtype, int* status,
-                  cudaStream_t stream) {
+                  int n_ident, cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (D <= 0 || F <= 0 || top <= 0 || n_experts <= 0 || il < 0 || (il > 0 && F % il) || !route_ids || !route_w) return ZK_EINVAL;
+  if (D <= 0 || F <= 0 || top <= 0 || n_experts <= 0 || n_ident < 0 || il < 0 || (il > 0 && F % il) || !route_ids || !route_w) return ZK_EINVAL;
   if (dtype == ZK_F32)
-    return launch_moe<float>(x, nullptr, route_ids, w_gu, il, w_down, h, y, n, D, F, top, 1, n_experts, accumulate, status, route_w, stream);
+    return launch_moe<float>(x, nullptr, route_ids, w_gu, il, w_down, h, y, n, D, F, top, 1, n_experts, accumulate, status, route_w, n_ident, stream);
   if (dtype == ZK_BF16)
-    return launch_moe<bf16>(x, nullptr, route_ids, w_gu, il, w_down, h, y, n, D, F, top, 1, n_experts, accumulate, status, route_w, stream);
+    return launch_moe<bf16>(x, nullptr, route_ids, w_gu, il, w_down, h, y, n, D, F, top, 1, n_experts, accumulate, status, route_w, n_ident, stream);
   return ZK_EINVAL;
 }
 
 // Router: z = W x_t in float32 (W [E, D] float32, x in the run dtype), s = softmax(z) over all experts, the `top`
-// largest s (ties: the lower index) are chosen and weighed s / (sum of the chosen + 1e-20).
+// largest s (ties: the lower index) are chosen and weighed s / (sum of the chosen + 1e-20).  With `correction` [E] the
+// choice goes by s + correction; the weights are made of s alone.
 int zk_moe_router(const void* x, const float* w_router, int* route_ids, float* route_w, int n, int D, int E, int top,
-                  int dtype, cudaStream_t stream) {
+                  int dtype, const float* correction, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (D <= 0 || E <= 0 || top <= 0 || top > E || E > MOE_ROUTER_MAX_EXPERTS) return ZK_EINVAL;
-  const size_t smem = sizeof(float) * ((size_t)D + E);
+  const size_t smem = sizeof(float) * ((size_t)D + 2 * (size_t)E);
   if (smem > 200 * 1024) return ZK_EINVAL;
 #define ZK_ROUTER(T)                                                                                                 \
   do {                                                                                                               \
@@ -426,7 +461,7 @@ int zk_moe_router(const void* x, const float* w_router, int* route_ids, float* r
       if (e != cudaSuccess) return (int)e;                                                                           \
     }                                                                                                                \
     return zk_launch_dependent(kern, dim3(n), dim3(MOE_WARPS * 32), smem, stream, (const T*)x, w_router, route_ids,  \
-                               route_w, D, E, top);                                                                  \
+                               route_w, D, E, top, correction);                                                      \
   } while (0)
   if (dtype == ZK_F32) ZK_ROUTER(float);
   if (dtype == ZK_BF16) ZK_ROUTER(bf16);
@@ -436,11 +471,11 @@ int zk_moe_router(const void* x, const float* w_router, int* route_ids, float* r
 
 // The device's own sort of (token, k) pairs by expert, as moe_expert_rows_kernel describes it.
 int zk_moe_expert_rows(const int* ids, int P, int E, int top, int tile, int cap, int* row_token, int* pair_row,
-                       int* tile_group, cudaStream_t stream) {
+                       int* tile_group, int n_ident, cudaStream_t stream) {
   if (P <= 0) return 0;
   if (E <= 0 || E > 4096 || top <= 0 || tile <= 0 || cap % tile || cap < (P / tile + E) * tile) return ZK_EINVAL;
   return zk_launch_dependent(moe_expert_rows_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * (size_t)E, stream, ids, P, E,
-                             top, tile, cap, row_token, pair_row, tile_group);
+                             top, tile, cap, row_token, pair_row, tile_group, n_ident);
 }
 
 // xg[r, :] = x[row_token[r], :] for r < n_rows, zeros where row_token[r] < 0 (rows in the run dtype, D elements).
@@ -457,10 +492,11 @@ int zk_moe_gather(const void* x, const int* row_token, void* xg, int n_rows, int
 
 // out[t, :] (=|+=) (1/top) * sum_k y[pair_row[t * top + k], :], float32, added in the order of k.
 int zk_moe_combine(const float* y, const int* pair_row, float* out, int n, int D, int top, int accumulate,
-                   const float* route_w, cudaStream_t stream) {
+                   const float* route_w, const void* x_ident, int x_dtype, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (D <= 0 || top <= 0) return ZK_EINVAL;
-  return zk_launch_dependent(moe_combine_kernel, dim3(n), dim3(128), 0, stream, y, pair_row, out, D, top, accumulate, route_w);
+  return zk_launch_dependent(moe_combine_kernel, dim3(n), dim3(128), 0, stream, y, pair_row, out, D, top, accumulate, route_w,
+                             x_ident, x_dtype == ZK_BF16 ? 1 : 0);
 }
 
 }  // extern "C"

@@ -28,10 +28,11 @@ _SIGNATURES = {
         "zk_rmsnorm": "ppppiifip",
         "zk_silu_mul": "ppiiiip",
         "zk_fill_normal": "pllffip",
-        "zk_rmsnorm_add": "pppiifp",
+        "zk_rmsnorm_add": "pppiiffp",
         "zk_activation": "ppliip",
         "zk_cast_rows": "pplip",
         "zk_softcap": "plfp",
+        "zk_scale": "plfp",
         "zk_weighted_sum": "ppilpp",
         "zk_gate_add": "ppppiiip",
         "zk_scale_add": "ppplip",
@@ -39,6 +40,9 @@ _SIGNATURES = {
         "zk_norm_shift": "pppplppppiiifiip",
         "zk_clamped_glu": "ppiiiffip",
         "zk_head_gate": "ppiiiiip",
+        "zk_layernorm": "pppppiifip",
+        "zk_value_gate": "ppiiiiiip",
+        "zk_unit_norm_gate": "ppipiiifip",
     },
     "latent": {
         "zk_latent_prepare": "pppi" + "ppppppp" + "iiiiii" + "f" + "iii" + "ppp",
@@ -49,6 +53,7 @@ _SIGNATURES = {
     "hgrn2": {
         "zk_hgrn2_scan": "pippplpppiiiiip",
         "zk_hgrn2_max_dim": "",
+        "zk_retention_scan": "pippifpplpppiiiiip",
     },
     "seqconv": {
         "zk_seqconv_forward": "ppppppp" + "iiiliiip",
@@ -58,10 +63,10 @@ _SIGNATURES = {
     "moe": {
         "zk_moe_table": "ppppippp" + "iiiiiiiipp",
         "zk_moe_gather": "pppiiip",
-        "zk_moe_combine": "pppiiii" + "p" + "p",
-        "zk_moe_routed": "ppppippp" + "iiiiiii" + "pp",
-        "zk_moe_router": "pppp" + "iiiii" + "p",
-        "zk_moe_expert_rows": "piiiiipppp",
+        "zk_moe_combine": "pppiiii" + "p" + "pi" + "p",
+        "zk_moe_routed": "ppppippp" + "iiiiiii" + "pip",
+        "zk_moe_router": "pppp" + "iiiii" + "pp",
+        "zk_moe_expert_rows": "piiiiippp" + "ip",
     },
     "gemm_simt": {
         "zk_gemm_simt": "ppppiiiiiiiiip",
@@ -93,7 +98,7 @@ _SIGNATURES = {
         "zk_attn_decode_noalloc_bytes": "iiii",
     },
     "attention_prefill": {
-        "zk_attn_prefill": "pppppppppp" + "iiiiiiiif" + "pp" + "pp" + "ip" + "p",
+        "zk_attn_prefill": "pppppppppp" + "iiiiiiiif" + "pp" + "pp" + "ip" + "f" + "p",
         "zk_attn_prefill_takes": "iiii",
         "zk_attn_prefill_tile_tokens": "ii",
     },
@@ -107,7 +112,7 @@ _SIGNATURES = {
         "zk_attn_decode_latent_takes": "iiii",
     },
     "attention_decode_tc": {
-        "zk_attn_decode_tc": "pppppppppiiiiiiifii" + "pp" + "i" + "ip" + "p",
+        "zk_attn_decode_tc": "pppppppppiiiiiiifii" + "pp" + "i" + "ip" + "f" + "p",
         "zk_attn_decode_tc_takes": "iiii",
     },
     "sampling": {
@@ -119,9 +124,9 @@ _SIGNATURES = {
         "zk_sample": "piififfffip" + "lpp" + "pp",
     },
     "attention": {
-        "zk_qk_prepare": "pppppppppppp" + "iiiiiiifiiip" + "ii" + "p",
+        "zk_qk_prepare": "pppppppppppp" + "iiiiiiifiiip" + "ii" + "fi" + "p",
         "zk_qk_prepare_span": "pipppppppppiiiiiifiiip" + "pi" + "p",
-        "zk_attn_fwd": "pppppp" + "pppppp" + "iiiiiiiifiiiii" + "ippi" + "ipi" + "p",
+        "zk_attn_fwd": "pppppp" + "pppppp" + "iiiiiiiifiiiii" + "ippi" + "ipi" + "f" + "p",
         "zk_attn_merge_talk": "ppppiiiiiip",
         "zk_attn_merge": "pppiiii" + "pi" + "p",
         "zk_attn_rows_per_block": "",
@@ -253,13 +258,14 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, status: torch.Tensor, scale
     return out
 
 
-def rmsnorm_add(m: torch.Tensor, weight: torch.Tensor, eps: float, x: torch.Tensor) -> torch.Tensor:
-    """x += RMSNorm(m) * weight, row by row, all float32: the norm of a sublayer's output summed into
-    the residual rows."""
+def rmsnorm_add(m: torch.Tensor, weight: torch.Tensor, eps: float, x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """x += scale * (RMSNorm(m) * weight), row by row, all float32: the norm of a sublayer's output (or a share of
+    it) summed into the residual rows."""
     _need(m, "m", torch.float32, (None, None))
     _need(x, "x", torch.float32, tuple(m.shape))
     _need(weight, "weight", torch.float32, (m.shape[1],))
-    _check(_fn("elementwise", "zk_rmsnorm_add")(_ptr(m), _ptr(weight), _ptr(x), m.shape[0], m.shape[1], eps, _stream()),
+    _check(_fn("elementwise", "zk_rmsnorm_add")(_ptr(m), _ptr(weight), _ptr(x), m.shape[0], m.shape[1], eps, float(scale),
+                                                _stream()),
            "rmsnorm_add")
     return x
 
@@ -295,6 +301,13 @@ def softcap(logits: torch.Tensor, cap: float) -> torch.Tensor:
     _need(logits, "logits", torch.float32)
     _check(_fn("elementwise", "zk_softcap")(_ptr(logits), logits.numel(), float(cap), _stream()), "softcap")
     return logits
+
+
+def scale_(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """x *= scale, in place; float32."""
+    _need(x, "x", torch.float32)
+    _check(_fn("elementwise", "zk_scale")(_ptr(x), x.numel(), float(scale), _stream()), "scale")
+    return x
 
 
 def weighted_sum(planes: torch.Tensor, weights: Optional[torch.Tensor], n_terms: int, out: torch.Tensor) -> torch.Tensor:
@@ -399,6 +412,33 @@ def hgrn2_scan(qfv: torch.Tensor, f_bias: torch.Tensor, lower: torch.Tensor, sta
     return o
 
 
+def retention_scan(qkv: torch.Tensor, decay: torch.Tensor, inv_freq: Optional[torch.Tensor], n_rot: int, key_scale: float,
+                   tok_pos, state: torch.Tensor, cu_q, seq_slot, n_seqs: int, n_heads: int, dim: int,
+                   value_dim: int) -> torch.Tensor:
+    """Per head S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t over each sequence's tokens, from the state the step
+    before left to the state this one leaves.  qkv float32 [n, >= 2*H*d + H*e] (row stride used), a row [q | k | v | ..]
+    as the projections gave them; q and k are overwritten: the first `n_rot` entries of every head rotated by the
+    token's position (half-split pairs, `inv_freq` float32 [n_rot / 2]; None = no rotation), k then times `key_scale`.
+    decay float32 [H]; state float32 [slots, H*d*e]; returns o float32 [n, H*e]."""
+    H, d, e = n_heads, dim, value_dim
+    _need(qkv, "qkv", torch.float32, (None, None), contiguous=False)
+    if qkv.shape[1] < 2 * H * d + H * e or qkv.stride(1) != 1:
+        raise KernelError(f"retention_scan: rows of {qkv.shape[1]} values hold no q, k and v of {H} heads")
+    _need(decay, "decay", torch.float32, (H,))
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32, (n_rot // 2,))
+    _need(state, "state", torch.float32, contiguous=False)
+    if state.dim() != 2 or state.shape[1] != H * d * e or state.stride(1) != 1:
+        raise KernelError(f"retention_scan: state {tuple(state.shape)} must hold {H * d * e} values per slot")
+    for t, nm in ((cu_q, "cu_q"), (seq_slot, "seq_slot"), (tok_pos, "tok_pos")):
+        _need(t, nm, torch.int32)
+    o = torch.empty((qkv.shape[0], H * e), dtype=torch.float32, device=qkv.device)
+    _check(_fn("hgrn2", "zk_retention_scan")(_ptr(qkv), qkv.stride(0), _ptr(decay), _ptr(inv_freq), int(n_rot), float(key_scale),
+                                             _ptr(tok_pos), _ptr(state), state.stride(0), _ptr(o), _ptr(cu_q), _ptr(seq_slot),
+                                             qkv.shape[0], n_seqs, H, d, e, _stream()), "retention_scan")
+    return o
+
+
 # ------------------------------------------------------------------------------- convolution over time on a mixer's input
 
 def seqconv_max_taps() -> int:
@@ -469,6 +509,55 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     y = torch.empty((n_out, dim), dtype=out_dtype, device=x.device)
     _check(_fn("elementwise", "zk_rmsnorm")(_ptr(x), _ptr(rows), _ptr(weight), _ptr(y), n_out, dim, eps,
                                             dtype_code(out_dtype), _stream()), "rmsnorm")
+    return y
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
+              rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Layer norm of float32 rows (all, or those listed in `rows`) into `out_dtype`: (x - mean) / sqrt(var + eps) *
+    weight + bias with var the mean of the squared deviations; `bias` None = none."""
+    _need(x, "x", torch.float32, (None, None))
+    dim = x.shape[1]
+    _need(weight, "weight", torch.float32, (dim,))
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (dim,))
+    n_out = x.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        n_out = rows.numel()
+    y = torch.empty((n_out, dim), dtype=out_dtype, device=x.device)
+    _check(_fn("elementwise", "zk_layernorm")(_ptr(x), _ptr(rows), _ptr(weight), _ptr(bias), _ptr(y), n_out, dim, eps,
+                                              dtype_code(out_dtype), _stream()), "layernorm")
+    return y
+
+
+def value_gate(rows: torch.Tensor, gate: torch.Tensor, n_heads: int, valid: int) -> torch.Tensor:
+    """rows[t, h, j] *= sigmoid(gate[t, h * valid + j]) for j < valid, in place.  rows [n, H * width] contiguous (run
+    dtype; the values of a head behind `valid` are padding and left alone); gate float32 [n, >= H * valid] (a view of
+    wider rows is fine: its row stride is used)."""
+    _need(rows, "rows", (torch.float32, torch.bfloat16), (None, None))
+    n, w = rows.shape
+    _need(gate, "gate", torch.float32, (n, None), contiguous=False)
+    if w % n_heads or valid > w // n_heads or gate.shape[1] < n_heads * valid or gate.stride(1) != 1:
+        raise KernelError(f"value_gate: rows {tuple(rows.shape)} / gate {tuple(gate.shape)} do not fit {n_heads} heads "
+                          f"of {valid} values")
+    _check(_fn("elementwise", "zk_value_gate")(_ptr(rows), _ptr(gate), gate.stride(0), n, n_heads, w // n_heads, valid,
+                                               dtype_code(rows.dtype), _stream()), "value_gate")
+    return rows
+
+
+def unit_norm_gate(o: torch.Tensor, gate: torch.Tensor, n_heads: int, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """y[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * silu(gate[t, h, :]): every head over its root mean
+    square (no weight), gated.  o float32 [n, H * e]; gate float32 [n, >= H * e] (may be a view of wider rows);
+    returns [n, H * e] in `out_dtype`."""
+    _need(o, "o", torch.float32, (None, None))
+    n, w = o.shape
+    _need(gate, "gate", torch.float32, (n, None), contiguous=False)
+    if w % n_heads or gate.shape[1] < w or gate.stride(1) != 1:
+        raise KernelError(f"unit_norm_gate: o {tuple(o.shape)} / gate {tuple(gate.shape)} do not fit {n_heads} heads")
+    y = torch.empty((n, w), dtype=out_dtype, device=o.device)
+    _check(_fn("elementwise", "zk_unit_norm_gate")(_ptr(o), _ptr(gate), gate.stride(0), _ptr(y), n, n_heads, w // n_heads,
+                                                   eps, dtype_code(out_dtype), _stream()), "unit_norm_gate")
     return y
 
 
@@ -936,40 +1025,51 @@ def moe_gather(x: torch.Tensor, row_token: torch.Tensor) -> torch.Tensor:
 
 
 def moe_combine(y: torch.Tensor, pair_row: torch.Tensor, top: int, out: torch.Tensor, accumulate: bool = False,
-                weights: Optional[torch.Tensor] = None) -> torch.Tensor:
+                weights: Optional[torch.Tensor] = None, identity_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t] (+)= sum_k weights[t, k] * y[pair_row[t * top + k]] (weights float32 [n, top]; without them 1/top
-    each), float32, added in the order of k."""
+    each), float32, added in the order of k.  A pair whose row is negative stands for an identity expert: its term is
+    identity_rows[t] (the rows the experts read, [n, D] in a run dtype)."""
     _need(y, "y", torch.float32, (None, None))
     _need(out, "out", torch.float32, (None, y.shape[1]))
     _need(pair_row, "pair_row", torch.int32, (out.shape[0] * top,))
     if weights is not None:
         _need(weights, "weights", torch.float32, (out.shape[0], top))
+    if identity_rows is not None:
+        _need(identity_rows, "identity_rows", (torch.float32, torch.bfloat16), (out.shape[0], y.shape[1]))
     _check(_fn("moe", "zk_moe_combine")(_ptr(y), _ptr(pair_row), _ptr(out), out.shape[0], y.shape[1], top,
-                                        1 if accumulate else 0, _ptr(weights), _stream()), "moe_combine")
+                                        1 if accumulate else 0, _ptr(weights), _ptr(identity_rows),
+                                        dtype_code(identity_rows.dtype) if identity_rows is not None else F32, _stream()),
+           "moe_combine")
     return out
 
 
-def moe_router(x: torch.Tensor, w_router: torch.Tensor, top: int) -> tuple[torch.Tensor, torch.Tensor]:
+def moe_router(x: torch.Tensor, w_router: torch.Tensor, top: int,
+               correction: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, torch.Tensor]:
     """(experts int32 [n, top], weights float32 [n, top]) of every row of x [n, D] (run dtype): logits W x in
     float32 (w_router float32 [E, D]), softmax over all E experts, the `top` largest scores (of equal ones the
-    lower index), each divided by the sum of the chosen (+ 1e-20)."""
+    lower index), each divided by the sum of the chosen (+ 1e-20).  `correction` float32 [E]: the choice goes by
+    score + correction, the weights are made of the scores alone."""
     _need(x, "x", (torch.float32, torch.bfloat16), (None, None))
     n, D = x.shape
     _need(w_router, "w_router", torch.float32, (None, D))
     E = w_router.shape[0]
+    if correction is not None:
+        _need(correction, "correction", torch.float32, (E,))
     if not 0 < top <= E:
         raise KernelError(f"moe_router: {top} experts per token out of {E}")
     ids = torch.empty((n, top), dtype=torch.int32, device=x.device)
     wts = torch.empty((n, top), dtype=torch.float32, device=x.device)
     _check(_fn("moe", "zk_moe_router")(_ptr(x), _ptr(w_router), _ptr(ids), _ptr(wts), n, D, E, top, dtype_code(x.dtype),
-                                       _stream()), "moe_router")
+                                       _ptr(correction), _stream()), "moe_router")
     return ids, wts
 
 
-def moe_expert_rows(route_ids: torch.Tensor, n_experts: int, tile: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+def moe_expert_rows(route_ids: torch.Tensor, n_experts: int, tile: int,
+                    n_identity: int = 0) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """The (token, k) pairs of route_ids [n, top] (int32, device) sorted by expert on the device, every expert's rows
     padded to whole tiles: (row_token [cap] with -1 for padding rows, pair_row [n * top], tile_group [cap / tile]),
-    cap = the most rows any choice can need.  Tiles behind the last expert's hold padding rows only."""
+    cap = the most rows any choice can need.  Tiles behind the last expert's hold padding rows only.  Ids n_experts ..
+    n_experts + n_identity - 1 name identity experts: such a pair gets no row (pair_row -1)."""
     _need(route_ids, "route_ids", torch.int32, (None, None))
     n, top = route_ids.shape
     P = n * top
@@ -977,15 +1077,16 @@ def moe_expert_rows(route_ids: torch.Tensor, n_experts: int, tile: int) -> tuple
     words = torch.empty(cap + P + cap // tile, dtype=torch.int32, device=route_ids.device)
     row_token, pair_row, tile_group = words[:cap], words[cap:cap + P], words[cap + P:]
     _check(_fn("moe", "zk_moe_expert_rows")(_ptr(route_ids), P, n_experts, top, tile, cap, _ptr(row_token), _ptr(pair_row),
-                                            _ptr(tile_group), _stream()), "moe_expert_rows")
+                                            _ptr(tile_group), int(n_identity), _stream()), "moe_expert_rows")
     return row_token, pair_row, tile_group
 
 
 def moe_routed(x: torch.Tensor, route_ids: torch.Tensor, route_w: torch.Tensor, w_gate_up: torch.Tensor, interleave: int,
                w_down: torch.Tensor, status: torch.Tensor, out: Optional[torch.Tensor] = None,
-               accumulate: bool = False) -> torch.Tensor:
+               accumulate: bool = False, n_identity: int = 0) -> torch.Tensor:
     """y[t] = sum_k route_w[t, k] * W_down[e] (silu(W_gate[e] x_t) * (W_up[e] x_t)), e = route_ids[t, k], added in
-    the order of k.  Tensors as in `moe_table`."""
+    the order of k.  Tensors as in `moe_table`.  Ids E .. E + n_identity - 1 name identity experts, whose term is
+    route_w[t, k] * x_t."""
     _need(x, "x", (torch.float32, torch.bfloat16), (None, None))
     n, D = x.shape
     _need(route_ids, "route_ids", torch.int32, (n, None))
@@ -1002,7 +1103,7 @@ def moe_routed(x: torch.Tensor, route_ids: torch.Tensor, route_w: torch.Tensor, 
     h = torch.empty((n, top, F), dtype=x.dtype, device=x.device)
     _check(_fn("moe", "zk_moe_routed")(_ptr(x), _ptr(route_ids), _ptr(route_w), _ptr(w_gate_up), int(interleave), _ptr(w_down),
                                        _ptr(h), _ptr(out), n, D, F, top, E, 1 if accumulate else 0, dtype_code(x.dtype),
-                                       _ptr(status), _stream()), "moe_routed")
+                                       _ptr(status), int(n_identity), _stream()), "moe_routed")
     return out
 
 
@@ -1131,11 +1232,15 @@ def attn_max_head_dim() -> int:
 
 def qk_prepare(qkv, k_cache, v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos, seq_slot, page_table, n_heads: int,
                n_kv: int, head_dim: int, n_rot: int, interleaved: bool, eps: float, status, write_kv: bool = True,
-               value_dim: Optional[int] = None, unit_norm_after: bool = False):
+               value_dim: Optional[int] = None, unit_norm_after: bool = False,
+               query_temperature: Optional[tuple] = None):
     """Per-head RMSNorm of q and k (if weights are given), rotary encoding (if `inv_freq` is
     given), then with `unit_norm_after` q and k heads divided by their root mean square (no weight);
     q out as [n, H*hd], and k, v written to their pages.  k_cache is one layer's
-    [pages, Hkv, page_size, hd], v_cache [pages, Hkv, page_size, value_dim (default hd)]."""
+    [pages, Hkv, page_size, hd], v_cache [pages, Hkv, page_size, value_dim (default hd)].
+    `query_temperature` = (coef, every): the query at position p is multiplied, last of all, by
+    1 + coef * ln(floor((p + 1) / every) + 1)."""
+    qt_coef, qt_every = (float(query_temperature[0]), int(query_temperature[1])) if query_temperature else (0.0, 0)
     vd = head_dim if value_dim is None else int(value_dim)
     _need(qkv, "qkv", (torch.float32, torch.bfloat16), (None, (n_heads + n_kv) * head_dim + n_kv * vd))
     n = qkv.shape[0]
@@ -1156,7 +1261,7 @@ def qk_prepare(qkv, k_cache, v_cache, q_w, k_w, inv_freq, tok_seq, tok_pos, seq_
         _ptr(qkv), _ptr(q), None, _ptr(k_cache), _ptr(v_cache), _ptr(q_w), _ptr(k_w), _ptr(inv_freq), _ptr(tok_seq),
         _ptr(tok_pos), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n, n_heads, n_kv, head_dim, n_rot,
         1 if interleaved else 0, eps, page_size, 1 if write_kv else 0, dtype_code(qkv.dtype), _ptr(status), vd,
-        1 if unit_norm_after else 0, _stream()),
+        1 if unit_norm_after else 0, qt_coef, qt_every, _stream()),
         "qk_prepare")
     return q
 
@@ -1203,7 +1308,8 @@ def qk_normed(qkv, q_w, k_w, n_heads: int, n_kv: int, head_dim: int, eps: float,
     dense = torch.empty_like(qkv)
     _check(_fn("attention", "zk_qk_prepare")(
         _ptr(qkv), None, _ptr(dense), None, None, _ptr(q_w), _ptr(k_w), None, None, _ptr(tok_pos), None, None, 0,
-        qkv.shape[0], n_heads, n_kv, head_dim, 0, 0, eps, 1, 0, dtype_code(qkv.dtype), _ptr(status), head_dim, 0, _stream()),
+        qkv.shape[0], n_heads, n_kv, head_dim, 0, 0, eps, 1, 0, dtype_code(qkv.dtype), _ptr(status), head_dim, 0, 0.0, 0,
+        _stream()),
         "qk_normed")
     return dense
 
@@ -1238,24 +1344,25 @@ def _takes(lib: str, fn: str, n_heads: int, n_kv: int, head_dim: int, page_size:
 def attention_plan(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int, page_size: int,
                    single_token: bool, window: int = 0, value_dim: Optional[int] = None,
                    biased: bool = False, talking: bool = False, extras: bool = False,
-                   kept_or_sink: bool = False) -> tuple[str, int]:
+                   kept_or_sink: bool = False, capped: bool = False) -> tuple[str, int]:
     """Which attention kernel runs for these sizes and how many tokens its query tiles hold:
     ("single_token_tc" | "single_token" | "prompt_tc5" | "prompt_tc" | "general", tokens per tile).
     Values of another width than the keys go to the general kernel; a distance bias on the scores is
     taken by the general kernel and the two mma.sync kernels ("prompt_tc", "single_token_tc"); weights that
     are mixed across the heads after the softmax (`talking`) by those three and the tcgen05 prompt kernel.
     `kept_or_sink`: kept first tokens or a sink in the softmax, which the general kernel and the two mma.sync kernels
-    take (without a bias or mixed weights); `extras`: values read from the key rows, the general kernel's."""
+    take (without a bias or mixed weights); `extras`: values read from the key rows, the general kernel's; `capped`:
+    scores through a tanh cap, which the same three kernels take."""
     same_width = value_dim is None or value_dim == head_dim
     if extras or (kept_or_sink and (biased or talking)):
         return "general", attn_tile_shape(n_heads, n_kv)[0]
     if same_width and dtype == torch.bfloat16 and n_heads % n_kv == 0:
-        if (not single_token and window <= 0 and not biased and not kept_or_sink and _may_take("attention_prefill_tc5", n_heads, n_kv, head_dim, page_size)
+        if (not single_token and window <= 0 and not biased and not kept_or_sink and not capped and _may_take("attention_prefill_tc5", n_heads, n_kv, head_dim, page_size)
                 and _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_takes")(n_heads, n_kv, head_dim, page_size, window)):
             return "prompt_tc5", _fn("attention_prefill_tc5", "zk_attn_prefill_tc5_tile_tokens")(n_heads, n_kv)
         if single_token and _takes("attention_decode_tc", "zk_attn_decode_tc_takes", n_heads, n_kv, head_dim, page_size):
             return "single_token_tc", 1
-        if (single_token and not biased and not talking and not kept_or_sink
+        if (single_token and not biased and not talking and not kept_or_sink and not capped
                 and _takes("attention_decode", "zk_attn_decode_takes", n_heads, n_kv, head_dim, page_size)):
             return "single_token", 1
         if not single_token and _takes("attention_prefill", "zk_attn_prefill_takes", n_heads, n_kv, head_dim, page_size):
@@ -1267,11 +1374,12 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
               head_dim: int, scale: float, window: int = 0, num_splits: int = 1, split_keys: int = 0,
               single_token: bool = False, kind: Optional[str] = None, value_dim: Optional[int] = None,
               bias: Optional[tuple] = None, talk: Optional[torch.Tensor] = None, keep_first: int = 0,
-              sink: Optional[torch.Tensor] = None, values_in_keys: bool = False) -> torch.Tensor:
+              sink: Optional[torch.Tensor] = None, values_in_keys: bool = False, softcap: float = 0.0) -> torch.Tensor:
     """Causal grouped-query attention of a packed batch against the paged cache.
     `keep_first`: with a window, the first so many positions of a sequence stay visible to every later query.
     `sink` float32 [H]: exp(sink_h) is one more term of head h's softmax denominator (no key, no value, not scaled).
     `values_in_keys`: there is no value cache; a value row is the first `value_dim` entries of the key row.
+    `softcap` > 0: a scaled score s becomes softcap * tanh(s / softcap) (the general kernel's and the two mma.sync kernels').
     The last is the general kernel's; the first two also the two mma.sync kernels' ("prompt_tc", "single_token_tc").  With
     num_splits > 1 the keys are cut at multiples of `split_keys` and merged afterwards.
     `single_token` says that every sequence brings exactly one query (row b = sequence b); the
@@ -1309,6 +1417,9 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
         _need(talk, "talk", torch.float32, (n_heads, n_heads))
         if kind not in (None, "general", "prompt_tc5", "prompt_tc", "single_token_tc"):
             raise KernelError(f"attention: the '{kind}' kernel mixes no weights across heads")
+    softcap = float(softcap or 0.0)
+    if softcap > 0 and kind not in (None, "general", "prompt_tc", "single_token_tc"):
+        raise KernelError(f"attention: the '{kind}' kernel caps no scores")
     if vd != head_dim and kind not in (None, "general"):
         raise KernelError(f"attention: the '{kind}' kernel takes no value width of its own")
     if bias is not None and kind not in (None, "general", "prompt_tc", "single_token_tc"):
@@ -1352,7 +1463,7 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq), _ptr(tile_q0), _ptr(cu_q),
             _ptr(seq_start), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n_tiles, n_heads, n_kv, head_dim,
             head_dim, page_size, window, scale, r1, r2, _ptr(part_o) if talk is not None else None,
-            _ptr(part_ml) if talk is not None else None, int(keep_first), _ptr(sink), _stream()),
+            _ptr(part_ml) if talk is not None else None, int(keep_first), _ptr(sink), softcap, _stream()),
             "attention (prompt, tensor cores)")
         return out if talk is None else _merge_talk(part_o, part_ml, talk, out, n, n_heads, n_kv, vd, 1)
     if (single_token and kind in (None, "single_token_tc") and q.dtype == torch.bfloat16
@@ -1360,7 +1471,8 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
         _check(_fn("attention_decode_tc", "zk_attn_decode_tc")(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(seq_start),
             _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n, n_heads, n_kv, head_dim, page_size, window,
-            scale, num_splits, split_keys, r1, r2, 1 if talk is not None else 0, int(keep_first), _ptr(sink), _stream()),
+            scale, num_splits, split_keys, r1, r2, 1 if talk is not None else 0, int(keep_first), _ptr(sink), softcap,
+            _stream()),
             "attention (single token, tensor cores)")
         if talk is not None:
             return _merge_talk(part_o, part_ml, talk, out, n, n_heads, n_kv, vd, num_splits)
@@ -1370,7 +1482,7 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
         return out
     if kind == "single_token_tc":
         raise KernelError("attention: the tensor-core single-token kernel does not take these sizes")
-    if (single_token and kind in (None, "single_token") and q.dtype == torch.bfloat16
+    if (single_token and kind in (None, "single_token") and q.dtype == torch.bfloat16 and softcap <= 0
             and _takes("attention_decode", "zk_attn_decode_takes", n_heads, n_kv, head_dim, page_size)):
         _check(_fn("attention_decode", "zk_attn_decode")(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(seq_start),
@@ -1384,7 +1496,7 @@ def attention(q, k_cache, v_cache, tile_seq, tile_q0, cu_q, seq_start, seq_slot,
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(tile_seq), _ptr(tile_q0),
         _ptr(cu_q), _ptr(seq_start), _ptr(seq_slot), _ptr(page_table), page_table.stride(0), n_tiles, n, n_heads, n_kv,
         head_dim, page_size, window, scale, bq, gc, num_splits, split_keys, dtype_code(q.dtype), vd, r1, r2,
-        1 if talk is not None else 0, int(keep_first), _ptr(sink), 1 if values_in_keys else 0, _stream()),
+        1 if talk is not None else 0, int(keep_first), _ptr(sink), 1 if values_in_keys else 0, softcap, _stream()),
         "attention")
     if talk is not None:
         return _merge_talk(part_o, part_ml, talk, out, n, n_heads, n_kv, vd, num_splits)
@@ -1405,12 +1517,15 @@ def attention_step_rows_tile_tokens(n_heads: int) -> int:
     return _fn("attention_prefill", "zk_attn_prefill_tile_tokens")(n_heads, n_heads)
 
 
-def attention_step_rows(q, k_rows, v_rows, tile_seq, tile_q0, cu_q, seq_start, seq_page0, n_heads: int, scale: float) -> torch.Tensor:
+def attention_step_rows(q, k_rows, v_rows, tile_seq, tile_q0, cu_q, seq_start, seq_page0, n_heads: int, scale: float,
+                        sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of a prompt step over keys and values that the step itself laid out (no cache): every head
     has keys and values of its own, k_rows [pages, H, page_size, head_dim] and v_rows [pages, H, page_size,
     value_dim], sequence b's position pos at row pos % page_size of page seq_page0[b] + pos // page_size.
     q [n, H * head_dim]; returns [n, H * value_dim].  bfloat16 on the tensor-core prompt kernel; the tiles hold
-    `attention_step_rows_tile_tokens` tokens."""
+    `attention_step_rows_tile_tokens` tokens.  `sink` float32 [H]: one more term of every head's softmax denominator."""
+    if sink is not None:
+        _need(sink, "sink", torch.float32, (n_heads,))
     _need(k_rows, "k_rows", torch.bfloat16, (None, n_heads, None, None))
     hd, page_size = k_rows.shape[3], k_rows.shape[2]
     _need(v_rows, "v_rows", torch.bfloat16, (k_rows.shape[0], n_heads, page_size, None))
@@ -1423,7 +1538,7 @@ def attention_step_rows(q, k_rows, v_rows, tile_seq, tile_q0, cu_q, seq_start, s
     _check(_fn("attention_prefill", "zk_attn_prefill")(
         _ptr(q), _ptr(k_rows), _ptr(v_rows), _ptr(out), _ptr(tile_seq), _ptr(tile_q0), _ptr(cu_q), _ptr(seq_start),
         _ptr(seq_page0), None, 0, tile_seq.numel(), n_heads, n_heads, hd, vd, page_size, 0, scale, None, None, None, None,
-        0, None, _stream()), "attention (prompt, a step's own rows)")
+        0, _ptr(sink), 0.0, _stream()), "attention (prompt, a step's own rows)")
     return out
 
 
@@ -1437,11 +1552,14 @@ def attention_latent_single_takes(dtype: torch.dtype, n_heads: int, row_dim: int
 
 
 def attention_latent_single(q, cache, seq_start, seq_slot, page_table, n_heads: int, value_dim: int, scale: float,
-                            num_splits: int = 1, split_keys: int = 0) -> torch.Tensor:
+                            num_splits: int = 1, split_keys: int = 0, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Single-token steps of attention over one cached row per token that is key and value at once: q [n, H * W]
     (sequence b's queries in row b), cache [pages, 1, page_size, W], a value = a row's first `value_dim` entries.
     Returns [n, H * value_dim].  bfloat16, on the tensor cores; with num_splits > 1 the keys are cut at multiples of
-    `split_keys` and merged afterwards."""
+    `split_keys` and merged afterwards.  `sink` float32 [H]: one more term of every head's softmax denominator, added
+    by the merge (which then runs for a single chunk too)."""
+    if sink is not None:
+        _need(sink, "sink", torch.float32, (n_heads,))
     _need(cache, "cache", torch.bfloat16, (None, 1, None, None))
     page_size, W = cache.shape[2], cache.shape[3]
     _need(q, "q", torch.bfloat16, (None, n_heads * W))
@@ -1450,16 +1568,16 @@ def attention_latent_single(q, cache, seq_start, seq_slot, page_table, n_heads: 
         raise KernelError(f"attention over latent rows: no kernel for rows of {W} with values of {value_dim}")
     out = torch.empty((n, n_heads * value_dim), dtype=q.dtype, device=q.device)
     part_o = part_ml = None
-    if num_splits > 1:
+    if num_splits > 1 or sink is not None:
         part_o = torch.empty((num_splits, n * n_heads, value_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((num_splits, n * n_heads, 2), dtype=torch.float32, device=q.device)
     _check(_fn("attention_decode_latent", "zk_attn_decode_latent")(
         _ptr(q), _ptr(cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(seq_start), _ptr(seq_slot), _ptr(page_table),
         page_table.stride(0), n, n_heads, W, value_dim, page_size, scale, num_splits, split_keys, _stream()),
         "attention (single token, latent rows)")
-    if num_splits > 1:
+    if part_o is not None:
         _check(_fn("attention", "zk_attn_merge")(_ptr(part_o), _ptr(part_ml), _ptr(out), n * n_heads, value_dim, num_splits,
-                                                 dtype_code(q.dtype), None, n_heads, _stream()), "attention merge")
+                                                 dtype_code(q.dtype), _ptr(sink), n_heads, _stream()), "attention merge")
     return out
 
 

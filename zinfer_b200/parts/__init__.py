@@ -11,7 +11,9 @@ from .latent import LatentAttention
 from .linear import linear
 from .loop import PassInput
 from .moe import RoutedMoE, TableMoE
-from .norm import RMSNorm
+from .norm import LayerNorm, RMSNorm
+from .pair import MixerPair
+from .retention import Retention
 from .rope import RotaryEncoding
 from .seqconv import InputConv
 from .shift import TokenShift

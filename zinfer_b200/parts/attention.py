@@ -22,6 +22,9 @@ sum_g T[h, g] * (weights of head g), and head h applies them to the values of it
 `keep_first` (with a window): the first so many tokens of a sequence stay visible to every later query, at their
 true positions; the cache keeps their pages.  `sink_name`: one learned number per head, [heads]; exp(sink_h) is
 one more term of head h's softmax denominator, with no key and no value, and is not scaled.
+`query_temperature` = (coef, every): the query at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)
+(positions enter through that factor alone when there is no position encoding).  `softcap`: a scaled score s becomes
+softcap * tanh(s / softcap) before the softmax.
 
 How the kernels are launched is decided here, not by the engine: the table of query tiles of a
 step, and for single-token steps the cut of a sequence's keys into chunks that separate blocks
@@ -95,7 +98,8 @@ class GqaAttention(Mixer):
                  scale: Optional[float] = None, split_keys: int = 0, value_dim: Optional[int] = None,
                  qk_norm_span: str = "head", distance_bias: Optional[tuple[str, str]] = None, own_kv: bool = True,
                  unit_norm_after_rotation: bool = False, talk_name: Optional[str] = None, keep_first: int = 0,
-                 sink_name: Optional[str] = None):
+                 sink_name: Optional[str] = None, query_temperature: Optional[tuple[float, int]] = None,
+                 softcap: Optional[float] = None):
         """split_keys: keys per chunk of single-token attention, a multiple of 64 (0 = chosen per
         step from the batch and the GPU's size)."""
         if n_heads % n_kv_heads:
@@ -116,6 +120,12 @@ class GqaAttention(Mixer):
             raise ValueError("attention: no kernel takes kept first tokens or a sink together with a distance bias or "
                              "weights mixed across heads")
         self.keep_first, self.sink_name, self.sink = int(keep_first), sink_name, None
+        if query_temperature is not None and (int(query_temperature[1]) <= 0 or qk_norm_span == "all" or not own_kv):
+            raise ValueError("attention: a query temperature needs a positive period and goes with per-head preparation")
+        self.query_temperature = None if query_temperature is None else (float(query_temperature[0]), int(query_temperature[1]))
+        if softcap is not None and (not softcap > 0 or talk_name is not None):
+            raise ValueError("attention: a score cap must be positive and does not go with weights mixed across heads")
+        self.softcap = 0.0 if softcap is None else float(softcap)
         if self.span_prepare and qk_norm_span == "head" and (q_norm_name or k_norm_name):
             raise ValueError("attention: per-head norms go with key/value weights of the mixer's own")
         if talk_name is not None and distance_bias is not None:
@@ -223,12 +233,13 @@ class GqaAttention(Mixer):
             q = kernels.qk_prepare(qkv, kv.k, kv.v, self.q_norm, self.k_norm, rot.inv_freq if rot else None,
                                    n_rot=rot.n_rot if rot else 0, interleaved=rot.interleaved if rot else False,
                                    write_kv=call.writes_kv, value_dim=self.value_dim,
-                                   unit_norm_after=self.unit_norm_after, **common)
+                                   unit_norm_after=self.unit_norm_after, query_temperature=self.query_temperature, **common)
         else:
             # A position encoding that is not a rotation table runs between the norm and the
             # cache write: norm in place of a copy of qkv, the encoding's own step, then the write.
-            if self.value_dim != self.head_dim:
-                raise ValueError("attention: a position encoding of its own needs values as wide as the keys")
+            if self.value_dim != self.head_dim or self.query_temperature is not None:
+                raise ValueError("attention: a position encoding of its own needs values as wide as the keys and takes "
+                                 "no query temperature")
             normed = kernels.qk_normed(qkv, self.q_norm, self.k_norm, self.n_heads, self.n_kv, self.head_dim, self.eps,
                                        ctx.tok_pos, ctx.status)
             self.position.apply(ctx, normed[:, :self.q_dim], normed[:, self.q_dim:self.q_dim + self.kv_dim])
@@ -237,7 +248,8 @@ class GqaAttention(Mixer):
         kind, tile_tokens = kernels.attention_plan(q.dtype, self.n_heads, self.n_kv, self.head_dim, kv.page_size,
                                                    ctx.is_decode, self.window, self.value_dim,
                                                    self.distance_bias is not None, self.talk_name is not None,
-                                                   kept_or_sink=self.keep_first > 0 or self.sink is not None)
+                                                   kept_or_sink=self.keep_first > 0 or self.sink is not None,
+                                                   capped=self.softcap > 0)
         tile_seq, tile_q0 = ctx.memo(("query tiles", tile_tokens), lambda: self._tiles_on_device(ctx, tile_tokens))
         num_splits, split_keys = (key_chunks(ctx.n_seqs, self.n_kv, ctx.max_kv_len, self._sm_count, self.split_keys)
                                   if ctx.is_decode else (1, 0))
@@ -246,7 +258,7 @@ class GqaAttention(Mixer):
                                 num_splits, split_keys, single_token=ctx.is_decode, kind=kind,
                                 value_dim=self.value_dim,
                                 bias=(self.bias_r1, self.bias_r2) if self.distance_bias is not None else None,
-                                talk=self.talk, keep_first=self.keep_first, sink=self.sink)
+                                talk=self.talk, keep_first=self.keep_first, sink=self.sink, softcap=self.softcap)
         linear(att, self.w_out, out=out, accumulate=accumulate)
 
 

@@ -3,8 +3,8 @@ src/model.zig:2352-2358, 466); logits = xn W_out^T in float32 with W_out the hea
 the embedding itself when tied (src/model.zig:595-598, 2490).
 
 Two options other designs use: a learned position table whose row for the token's position is
-added to the embedding (unscaled, float32), and a soft cap on the logits,
-logits <- cap * tanh(logits / cap)."""
+added to the embedding (unscaled, float32), a soft cap on the logits,
+logits <- cap * tanh(logits / cap), and a constant the logits are multiplied by (`scale`, applied last)."""
 from __future__ import annotations
 
 import torch
@@ -43,13 +43,14 @@ class LMHead(Part):
     """`weight_name` None ties the head to `embedding`."""
 
     def __init__(self, vocab: int, dim: int, weight_name: str | None, embedding: TokenEmbedding | None = None,
-                 softcap: float | None = None):
+                 softcap: float | None = None, scale: float = 1.0):
         if weight_name is None and embedding is None:
             raise ValueError("a tied head needs the embedding it is tied to")
         if softcap is not None and not softcap > 0:
             raise ValueError(f"a logit cap must be positive, got {softcap}")
         self.vocab, self.dim, self.weight_name, self.embedding = vocab, dim, weight_name, embedding
         self.softcap = None if softcap is None else float(softcap)
+        self.scale = float(scale)
         self.weight = None
 
     def weight_specs(self):
@@ -66,4 +67,6 @@ class LMHead(Part):
         logits = linear(xn, w, out=out, out_dtype=torch.float32)
         if self.softcap is not None:
             kernels.softcap(logits, self.softcap)
+        if self.scale != 1.0:
+            kernels.scale_(logits, self.scale)
         return logits

@@ -23,7 +23,12 @@ d + p multiplications a score instead of r + p.  The cache rows are written all 
 A prompt step that CONTINUES its sequences (a later portion of a long prompt) does the same over all their tokens:
 the cached latents are packed and expanded once more, and the shared key part is read back from the cache rows.
 
-The output gate is optional (`gate_name` None = none), as is the query latent (`q_down_name` None: q = W_uq h)."""
+The output gate is optional (`gate_name` None = none), as is the query latent (`q_down_name` None: q = W_uq h).
+Options other designs use: `gate_per_value` (the gate has a logit for every output value, W_g [H * e, width], instead of
+one per head); `sink_name` (one learned number per head; exp(sink_h) is one more term of head h's softmax denominator,
+with no key and no value, not scaled); `interleaved` (the rotated part pairs entry 2i with entry 2i + 1 instead of i
+with i + p/2: since the rotated query and key parts only ever meet in a dot product, the rows of W_uq and W_dkv that
+make them are reordered once at load, pairs (2i, 2i + 1) -> (i, i + p/2), and every kernel rotates half-split pairs)."""
 from __future__ import annotations
 
 from typing import Optional
@@ -50,7 +55,8 @@ class LatentAttention(Mixer):
     def __init__(self, hidden: int, n_heads: int, dim: int, rot_dim: int, value_dim: int, kv_rank: int, q_rank: Optional[int],
                  scale: float, rot_base: float, q_down_name: Optional[str], q_norm_name: Optional[str], q_up_name: str,
                  kv_down_name: str, kv_norm_name: str, k_up_name: str, v_up_name: str, out_name: str,
-                 gate_name: Optional[str] = None, norm_eps: float = 1e-5, split_keys: int = 0):
+                 gate_name: Optional[str] = None, norm_eps: float = 1e-5, split_keys: int = 0, gate_per_value: bool = False,
+                 sink_name: Optional[str] = None, interleaved: bool = False):
         if rot_dim <= 0 or rot_dim % 2:
             raise ValueError(f"latent attention: the rotated width {rot_dim} must be even and positive")
         if (q_down_name is None) != (q_rank is None) or (q_down_name is None) != (q_norm_name is None):
@@ -60,6 +66,8 @@ class LatentAttention(Mixer):
         self.q_down_name, self.q_norm_name, self.q_up_name = q_down_name, q_norm_name, q_up_name
         self.kv_down_name, self.kv_norm_name, self.k_up_name, self.v_up_name = kv_down_name, kv_norm_name, k_up_name, v_up_name
         self.out_name, self.gate_name, self.split_keys = out_name, gate_name, int(split_keys)
+        self.gate_per_value, self.sink_name, self.interleaved = bool(gate_per_value) and gate_name is not None, sink_name, bool(interleaved)
+        self.sink = None
         self.w_dq = self.w_down = self.w_uq = self.w_uk_t = self.w_uv = self.w_out = self.q_norm = self.c_norm = self.inv_freq = None
         self._sm_count = 0
 
@@ -78,18 +86,28 @@ class LatentAttention(Mixer):
             specs += [WeightSpec(self.q_down_name, (self.q_rank, D)),
                       WeightSpec(self.q_norm_name, (self.q_rank,), role="vector", init="norm")]
         if self.gate_name is not None:
-            specs.append(WeightSpec(self.gate_name, (H, D)))
+            specs.append(WeightSpec(self.gate_name, (H * e if self.gate_per_value else H, D)))
+        if self.sink_name is not None:
+            specs.append(WeightSpec(self.sink_name, (H,), role="vector"))
         return specs
 
     def load(self, weights, dtype, device):
         H, d, e, r = self.n_heads, self.dim, self.value_dim, self.kv_rank
         # the key/value latent, the shared key part and the gate's logits are one contraction with a float32 result
         self.w_dq = weights[self.q_down_name] if self.q_down_name is not None else None
-        down = [weights[self.kv_down_name]]
+        w_uq, w_dkv = weights[self.q_up_name], weights[self.kv_down_name]
+        if self.interleaved:        # pairs (2i, 2i + 1) of the rotated parts become pairs (i, i + p/2)
+            p = self.rot_dim
+            order = torch.cat([torch.arange(0, p, 2), torch.arange(1, p, 2)]).to(w_uq.device)
+            w_uq = w_uq.reshape(H, d + p, -1)
+            w_uq = torch.cat([w_uq[:, :d], w_uq[:, d:][:, order]], dim=1).reshape(H * (d + p), -1).contiguous()
+            w_dkv = torch.cat([w_dkv[:r], w_dkv[r:][order]], dim=0).contiguous()
+        down = [w_dkv]
         if self.gate_name is not None:
             down.append(weights[self.gate_name])
         self.w_down = torch.cat(down, dim=0).contiguous()
-        self.w_uq = weights[self.q_up_name]
+        self.w_uq = w_uq
+        self.sink = weights[self.sink_name].contiguous() if self.sink_name is not None else None
         self.w_uk_t = weights[self.k_up_name].reshape(H, d, r).transpose(1, 2).contiguous()      # [H, r, d]
         self.w_uv = weights[self.v_up_name].reshape(H, e, r).contiguous()                         # [H, e, r]
         self.w_out = weights[self.out_name]
@@ -139,7 +157,8 @@ class LatentAttention(Mixer):
             cq = kernels.rmsnorm(linear(x, self.w_dq, out_dtype=torch.float32), self.q_norm, self.eps, ctx.dtype)
         q = linear(cq, self.w_uq)                                      # [n, H * (d + p)]
         dkv = low[:, :r + p]
-        gate = low[:, r + p:r + p + H] if self.gate_name is not None else None
+        gate = low[:, r + p:] if self.gate_name is not None else None
+        head_gate = None if self.gate_per_value else gate           # what the per-head products apply in their epilogue
         if (self.w_ukv is not None and ctx.starts is not None and not ctx.is_decode and call.writes_kv
                 and ctx.n_tokens >= EXPAND_MIN_SHARE * sum(s + l for s, l in zip(ctx.starts, ctx.q_lens))
                 and kernels.attention_step_rows_takes(q.dtype, self.key_width, self.value_width, kv.page_size)):
@@ -151,9 +170,11 @@ class LatentAttention(Mixer):
         if ctx.is_decode and kernels.attention_latent_single_takes(q.dtype, H, r + p, r, kv.page_size):
             num_splits, split_keys = key_chunks(ctx.n_seqs, 1, ctx.max_kv_len, self._sm_count, self.split_keys)
             lat = kernels.attention_latent_single(q_full, kv.k, ctx.seq_start, ctx.seq_slot, kv.page_table, H, r, self.scale,
-                                                  num_splits, split_keys)
+                                                  num_splits, split_keys, sink=self.sink)
             att = torch.empty((n, H * e), dtype=q.dtype, device=q.device)
-            self._per_head(lat, r, self.w_uv, att, e, gate)
+            self._per_head(lat, r, self.w_uv, att, e, head_gate)
+            if self.gate_per_value:
+                kernels.value_gate(att, gate, H, e)
             linear(att, self.w_out, out=out, accumulate=accumulate)
             return
         kind, tile_tokens = kernels.attention_plan(q.dtype, H, 1, r + p, kv.page_size, ctx.is_decode, 0, r, False, False, True)
@@ -163,9 +184,11 @@ class LatentAttention(Mixer):
                                   if ctx.is_decode else (1, 0))
         lat = kernels.attention(q_full, kv.k, None, tile_seq, tile_q0, ctx.cu_q, ctx.seq_start, ctx.seq_slot, kv.page_table,
                                 H, 1, r + p, self.scale, 0, num_splits, split_keys, single_token=ctx.is_decode, kind=kind,
-                                value_dim=r, values_in_keys=True)      # [n, H * r]: the weighted sums of the latents
+                                value_dim=r, values_in_keys=True, sink=self.sink)   # [n, H * r]: the weighted sums of the latents
         att = torch.empty((n, H * e), dtype=q.dtype, device=q.device)
-        self._per_head(lat, r, self.w_uv, att, e, gate)
+        self._per_head(lat, r, self.w_uv, att, e, head_gate)
+        if self.gate_per_value:
+            kernels.value_gate(att, gate, H, e)
         linear(att, self.w_out, out=out, accumulate=accumulate)
 
 
@@ -202,8 +225,11 @@ class LatentAttention(Mixer):
         tile_tokens = kernels.attention_step_rows_tile_tokens(H)
         from .attention import GqaAttention
         tile_seq, tile_q0 = ctx.memo(("query tiles", tile_tokens), lambda: GqaAttention._tiles_on_device(ctx, tile_tokens))
-        att = kernels.attention_step_rows(q_pad, k_rows, v_rows, tile_seq, tile_q0, ctx.cu_q, ctx.seq_start, first, H, self.scale)
-        if gate is not None:
+        att = kernels.attention_step_rows(q_pad, k_rows, v_rows, tile_seq, tile_q0, ctx.cu_q, ctx.seq_start, first, H, self.scale,
+                                          sink=self.sink)
+        if self.gate_per_value:
+            kernels.value_gate(att, gate, H, e)
+        elif gate is not None:
             kernels.head_gate(att, gate, H)
         linear(att, self.w_out_wide, out=out, accumulate=accumulate)
 

@@ -39,7 +39,20 @@ def expert_rows(experts: np.ndarray, n_experts: int, top: int, tile: int = 1):
     """For the expert of every (token, k) pair, flat in the order t * top + k: (row_token [rows]: the token of each
     row when the pairs are sorted by expert, keeping their order within an expert, -1 for a padding row; pair_row
     [n * top]: the row each pair went to; bounds [experts + 1]: expert e owns rows bounds[e] .. bounds[e + 1]).
-    Every expert's rows are padded to a multiple of `tile`."""
+    Every expert's rows are padded to a multiple of `tile`.  An id of `n_experts` or more names an identity expert:
+    such a pair gets no row (pair_row -1)."""
+    experts = np.asarray(experts)
+    if experts.size and experts.max() >= n_experts:
+        real = np.flatnonzero(experts < n_experts)
+        row_token, rows_of_real, bounds = _expert_rows(experts[real], real // top, n_experts, tile)
+        pair_row = np.full(experts.size, -1, dtype=np.int32)
+        pair_row[real] = rows_of_real
+        return row_token, pair_row, bounds
+    return _expert_rows(experts, np.arange(experts.size) // top, n_experts, tile)
+
+
+def _expert_rows(experts: np.ndarray, tokens: np.ndarray, n_experts: int, tile: int):
+    """`expert_rows` for pairs that all name real experts; tokens[i] is the token of pair i."""
     order = np.argsort(experts, kind="stable")
     counts = np.bincount(experts, minlength=n_experts)
     padded = -(-counts // tile) * tile
@@ -49,7 +62,7 @@ def expert_rows(experts: np.ndarray, n_experts: int, top: int, tile: int = 1):
     np.cumsum(counts[:-1], out=starts[1:])
     rows = np.arange(order.size) + np.repeat(bounds[:-1] - starts, counts)     # row of each pair, in sorted order
     row_token = np.full(int(bounds[-1]), -1, dtype=np.int32)
-    row_token[rows] = order // top
+    row_token[rows] = tokens[order]
     pair_row = np.empty(order.size, dtype=np.int32)
     pair_row[order] = rows
     return row_token, pair_row, bounds
@@ -186,7 +199,8 @@ class TableMoE(FeedForward):
                 r0, r1 = int(bounds[e]), int(bounds[e + 1])
                 if r1 > r0:
                     ff.forward(ctx, xg[r0:r1], y[r0:r1], False)
-        kernels.moe_combine(y, pair_row, self.top, out, accumulate, weights)
+        kernels.moe_combine(y, pair_row, self.top, out, accumulate, weights,
+                            identity_rows=rows if getattr(self, "n_identity", 0) else None)
 
 
 class RoutedMoE(TableMoE):
@@ -199,24 +213,42 @@ class RoutedMoE(TableMoE):
     weight-streaming kernels read them there, so a single-token step needs nothing from the host and can be
     recorded.  Many tokens (prompt steps): a kernel sorts the rows by expert, every expert's rows padded to whole
     tiles, and the grouped tensor-core contractions of `TableMoE` run them; where those do not take the sizes, the
-    chosen ids come to the host once per call and the experts run one after the other."""
+    chosen ids come to the host once per call and the experts run one after the other.
+
+    Options other designs use.  `correction_name`: a vector [router outputs] that is added to the scores for the CHOICE
+    only; the weights are made of the scores alone.  `n_identity`: the router has that many outputs more than there are
+    experts with weights, and its last `n_identity` outputs stand for identity experts, whose result is the row they
+    read (times the weight); `top` may then exceed nothing but the router's outputs.  `shared`: a feed-forward every
+    token takes, added with weight 1."""
 
     takes_residual_rows = False
     takes_pending_norm = True
 
-    def __init__(self, hidden: int, ffn_dim: int, n_experts: int, top: int, router_name: str, expert_names):
-        super().__init__(hidden, ffn_dim, n_experts, top, 1, "", expert_names)
+    def __init__(self, hidden: int, ffn_dim: int, n_experts: int, top: int, router_name: str, expert_names,
+                 correction_name: Optional[str] = None, n_identity: int = 0, shared: Optional[FeedForward] = None):
+        if n_identity < 0 or not 0 < top <= n_experts + n_identity:
+            raise ValueError(f"{top} experts per token out of {n_experts} and {n_identity} identity experts")
+        super().__init__(hidden, ffn_dim, n_experts, min(top, n_experts), 1, "", expert_names, shared=shared)
+        self.top = top
         self.router_name, self.w_router = router_name, None
+        self.correction_name, self.correction, self.n_identity = correction_name, None, int(n_identity)
+
+    @property
+    def n_router(self) -> int:
+        return self.n_experts + self.n_identity
 
     def weight_specs(self):
         F, D = self.ffn_dim, self.hidden
-        specs = [WeightSpec(self.router_name, (self.n_experts, D), role="vector")]      # kept in float32
+        specs = [WeightSpec(self.router_name, (self.n_router, D), role="vector")]      # kept in float32
+        if self.correction_name is not None:
+            specs.append(WeightSpec(self.correction_name, (self.n_router,), role="vector"))
         for g, u, d in self.names:
             specs += [WeightSpec(g, (F, D)), WeightSpec(u, (F, D)), WeightSpec(d, (D, F))]
         return specs
 
     def load(self, weights, dtype, device):
         self.w_router = weights[self.router_name].contiguous()
+        self.correction = weights[self.correction_name].contiguous() if self.correction_name is not None else None
         stack = (lambda g, u: interleave_rows([g, u])) if self.interleave else (lambda g, u: torch.cat([g, u], dim=0))
         self.w_gate_up = torch.stack([stack(weights[g], weights[u]) for g, u, _ in self.names]).contiguous()
         self.w_down = torch.stack([weights[d] for _, _, d in self.names]).contiguous()
@@ -231,23 +263,28 @@ class RoutedMoE(TableMoE):
         rows = as_tensor(xn)
         if rows.dtype != ctx.dtype:
             rows = kernels.cast_rows(rows, ctx.dtype)
-        ids, wts = kernels.moe_router(rows, self.w_router, self.top)
+        self._experts(ctx, rows, out, accumulate)
+        if self.shared is not None:
+            self.shared.forward(ctx, rows, out, True)
+
+    def _experts(self, ctx, rows, out, accumulate):
+        ids, wts = kernels.moe_router(rows, self.w_router, self.top, self.correction)
         if ctx.is_decode or rows.shape[0] < GROUPED_MIN_TOKENS:
             kernels.moe_routed(rows, ids, wts, self.w_gate_up, self.interleave, self.w_down, ctx.status, out=out,
-                               accumulate=accumulate)
+                               accumulate=accumulate, n_identity=self.n_identity)
             return
         tile = kernels.GEMM_TC_GROUP_ROWS
         if (self.interleave and rows.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.ffn_dim % 8 == 0
                 and rows.is_contiguous() and self.n_experts <= 4096):
             # the rows are sorted by expert where the router left its choice: the step never waits for the host
-            row_token, pair_row, tile_group = kernels.moe_expert_rows(ids, self.n_experts, tile)
+            row_token, pair_row, tile_group = kernels.moe_expert_rows(ids, self.n_experts, tile, self.n_identity)
             xg = kernels.moe_gather(rows, row_token)
             h = kernels.gemm_tc_grouped(xg, self.w_gate_up, tile_group, swiglu=True)
             y = kernels.gemm_tc_grouped(h, self.w_down, tile_group, out_dtype=torch.float32)
-            kernels.moe_combine(y, pair_row, self.top, out, accumulate, wts)
+            kernels.moe_combine(y, pair_row, self.top, out, accumulate, wts, identity_rows=rows if self.n_identity else None)
             return
         chosen = ids.cpu().numpy().reshape(-1).astype(np.int64)
-        self._expert_by_expert(ctx, rows, None, out, accumulate, chosen=np.clip(chosen, 0, self.n_experts - 1), weights=wts)
+        self._expert_by_expert(ctx, rows, None, out, accumulate, chosen=np.clip(chosen, 0, self.n_router - 1), weights=wts)
 
 
 FEED_FORWARDS.register("table_moe", TableMoE)

@@ -1,5 +1,5 @@
 """RMSNorm: y = x * 1/sqrt(mean(x^2) + eps) * w, sum and scale in float32
-(src/model.zig:1166-1181; plain weight, no 1 + w)."""
+(src/model.zig:1166-1181; plain weight, no 1 + w); and the layer norm with weight and bias that other designs use."""
 from __future__ import annotations
 
 from typing import Optional
@@ -47,4 +47,28 @@ class RMSNorm(Norm):
         return ResidualSink(x, self.weight)
 
 
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(var + eps) * w + b over a row, var the mean of the squared deviations; sums and scale in
+    float32.  `bias_name` None: no bias.  It has no pending form: every consumer gets the normalised tensor."""
+
+    def __init__(self, dim: int, eps: float, weight_name: str, bias_name: Optional[str] = None):
+        self.dim, self.eps, self.weight_name, self.bias_name = dim, float(eps), weight_name, bias_name
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def weight_specs(self):
+        specs = [WeightSpec(self.weight_name, (self.dim,), role="vector", init="norm")]
+        if self.bias_name is not None:
+            specs.append(WeightSpec(self.bias_name, (self.dim,), role="vector"))
+        return specs
+
+    def load(self, weights, dtype, device):
+        self.weight = weights[self.weight_name]
+        self.bias = weights[self.bias_name] if self.bias_name is not None else None
+
+    def forward(self, ctx, x, rows=None):
+        return kernels.layernorm(x, self.weight, self.bias, self.eps, ctx.dtype, rows)
+
+
 NORMS.register("rmsnorm", RMSNorm)
+NORMS.register("layernorm", LayerNorm)
