@@ -142,26 +142,32 @@ def gated_unit(h, gate, up, down):
 
 
 def route(z, correction, top):
-    """Softmax scores of the logits z [experts]; the `top` experts with the largest score + correction, and their
-    weights: the scores without the correction, over their sum."""
+    """Softmax scores of the logits z [experts]; the `top` experts with the largest score + correction, their
+    weights (the scores without the correction, over their sum), and the margin of the choice: how far the last chosen
+    expert's score + correction lies above the best one that was not chosen (inf when all are chosen)."""
     s = np.exp(z - z.max())
     s = s / s.sum()
     pick = s + correction if correction is not None else s
-    chosen = sorted(range(len(z)), key=lambda i: (-pick[i], i))[:top]
+    ranked = sorted(range(len(z)), key=lambda i: (-pick[i], i))
+    chosen = ranked[:top]
     total = sum(s[i] for i in chosen) + 1e-20
-    return chosen, [s[i] / total for i in chosen]
+    margin = pick[ranked[top - 1]] - pick[ranked[top]] if top < len(z) else np.inf
+    return chosen, [s[i] / total for i in chosen], margin
 
 
-def experts(h, W, ml):
+def experts(h, W, ml, margins=None):
     """Routed experts; the last `identity` outputs of the router stand for experts that return their input; a shared
-    expert every token takes.  W: router, correction, e<i>.gate/up/down, shared.gate/up/down."""
+    expert every token takes.  W: router, correction, e<i>.gate/up/down, shared.gate/up/down.  `margins`: a list with
+    one entry per token that is lowered to the token's margin of choice (see `route`)."""
     n = h.shape[0]
     ro = ml["router"]
     E, ident, top = ro["experts"], ro.get("identity", 0), ro["top"]
     out = np.zeros_like(h)
     z = h @ W["router"].T
     for t in range(n):
-        chosen, wts = route(z[t], W.get("correction"), top)
+        chosen, wts, margin = route(z[t], W.get("correction"), top)
+        if margins is not None:
+            margins[t] = min(margins[t], margin)
         for i, w in zip(chosen, wts):
             if i >= E:
                 out[t] += w * h[t]
@@ -180,9 +186,10 @@ def layer_runs(cfg):
     return (list(range(lp["start"])) + list(range(lp["start"], lp["stop"])) * lp["times"] + list(range(lp["stop"], n)))
 
 
-def forward(cfg, W, tokens, taps=None):
+def forward(cfg, W, tokens, taps=None, margins=None):
     """Logits [n, vocab] of one sequence.  W: name -> float64 array.  `taps`: a list that receives the rows after
-    every layer run."""
+    every layer run.  `margins`: a list with one entry per token, lowered to the smallest margin of any expert choice
+    made for that token."""
     eps = cfg["norm"]["eps"]
     x = W["embed"][np.asarray(tokens)].astype(np.float64)
     for i in layer_runs(cfg):
@@ -197,7 +204,7 @@ def forward(cfg, W, tokens, taps=None):
             raise ValueError(L["type"])
         if L.get("mlp") is not None:
             fw = {k[len(pre) + 4:]: v for k, v in W.items() if k.startswith(pre + "mlp.")}
-            y = y + experts(h, fw, L["mlp"])
+            y = y + experts(h, fw, L["mlp"], margins)
         x = x + y
         if taps is not None:
             taps.append(x.copy())

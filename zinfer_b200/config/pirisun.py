@@ -182,6 +182,9 @@ class PirisunConfig(ModelConfig):
             if kind == "latent_attention":
                 layers.append(PirisunLayer(kind, latent=_latent(m, w), mlp=mlp))
             elif kind == "parallel":
+                for side in ("left", "right"):
+                    if not _obj(m, side, w):
+                        raise ConfigError(f"config.json: required key '{w}{side}' is missing")
                 layers.append(PirisunLayer(kind, left=_left(_obj(m, "left", w), w + "left."),
                                            right=_right(_obj(m, "right", w), w + "right."), mlp=mlp))
             else:
