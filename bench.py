@@ -340,15 +340,70 @@ def ponusun_like_kerotar(sz: dict) -> dict:
             "norm": {"eps": 1e-5}, "layers": layers}
 
 
+# Pirisun beside the closest existing architecture at equal size, Kerotar (parallel layers, attention through a latent,
+# routed experts): width, layers, vocabulary, heads, the latent's sizes and the experts are the same.  Where Kerotar has
+# grouped-query attention with a sink (here without a window, so that both attend to every earlier token), Pirisun has
+# its pair of mixers: attention with capped scores and a query temperature beside retention; its latent attention has
+# no query latent but a sink and a gate per value; its router has a correction and two identity experts, and every
+# layer also runs a shared expert.
+PIRISUN_SIZES = {
+    "w1024": dict(width=1024, layers=8, heads=16, kv=4, dim=64, ret_heads=8, ret_dim=128, lat_dim=64, lat_rot=32, lat_vdim=64,
+                  kv_rank=256, q_rank=512, experts=16, top=2, identity=2, ff=1024, shared=1024, vocab=32768),
+    "w2048": dict(width=2048, layers=8, heads=32, kv=8, dim=64, ret_heads=16, ret_dim=128, lat_dim=64, lat_rot=32, lat_vdim=64,
+                  kv_rank=512, q_rank=768, experts=16, top=2, identity=2, ff=2048, shared=2048, vocab=65536),
+}
+
+
+def pirisun_config(sz: dict) -> dict:
+    layers = []
+    for i in range(sz["layers"]):
+        if i % 2 == 0:
+            kind = "parallel"
+            mixer = {"left": {"heads": sz["heads"], "kv_heads": sz["kv"], "dim": sz["dim"], "vdim": sz["dim"], "scale": sz["dim"] ** -0.5,
+                              "softcap": 30.0, "q_temp": {"coef": 0.3, "every": 128}},
+                     "right": {"heads": sz["ret_heads"], "dim": sz["ret_dim"], "vdim": sz["width"] // sz["ret_heads"],
+                               "decay": [1.0 - 2.0 ** -(5 + h % 6) for h in range(sz["ret_heads"])],
+                               "rot": {"base": 1000000.0, "dims": sz["ret_dim"]}}}
+        else:
+            kind = "latent_attention"
+            mixer = {"heads": sz["heads"], "dim": sz["lat_dim"], "rot_dim": sz["lat_rot"], "vdim": sz["lat_vdim"],
+                     "kv_rank": sz["kv_rank"], "scale": (sz["lat_dim"] + sz["lat_rot"]) ** -0.5,
+                     "rot": {"base": 10000.0, "dims": sz["lat_rot"]}}
+        mlp = {"kind": "moe", "expert": {"ff": sz["ff"]}, "shared": {"ff": sz["shared"]},
+               "router": {"experts": sz["experts"], "top": sz["top"], "identity": sz["identity"]}}
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Pirisun", "vocab": sz["vocab"], "width": sz["width"], "max_positions": CONTEXT,
+            "norm": {"eps": 1e-5}, "logit_scale": 1.0, "layers": layers}
+
+
+def kerotar_like_pirisun(sz: dict) -> dict:
+    layers = []
+    for i in range(sz["layers"]):
+        if i % 2 == 0:
+            kind = "attention"
+            mixer = {"heads": sz["heads"], "kv_heads": sz["kv"], "dim": sz["dim"], "vdim": sz["dim"], "scale": sz["dim"] ** -0.5,
+                     "rot": {"base": 10000.0, "dims": sz["dim"] // 2}}
+        else:
+            kind = "latent_attention"
+            mixer = {"heads": sz["heads"], "dim": sz["lat_dim"], "rot_dim": sz["lat_rot"], "vdim": sz["lat_vdim"],
+                     "kv_rank": sz["kv_rank"], "q_rank": sz["q_rank"], "scale": (sz["lat_dim"] + sz["lat_rot"]) ** -0.5,
+                     "rot": {"base": 10000.0, "dims": sz["lat_rot"]}}
+        mlp = {"kind": "moe", "expert": {"ff": sz["ff"]}, "router": {"experts": sz["experts"], "top": sz["top"]}}
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Kerotar", "vocab": sz["vocab"], "width": sz["width"], "max_positions": CONTEXT,
+            "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "layers": layers}
+
+
 # new architecture -> (sizes, its configuration, the configuration of the architecture beside it, that one's name)
 COMPARISONS = {"ponusun": (PONUSUN_SIZES, ponusun_config, lfm2_like, "lfm2"),
                "zosurax": (ZOSURAX_SIZES, zosurax_config, lfm2_like_zosurax, "lfm2"),
-               "kerotar": (KEROTAR_SIZES, kerotar_config, ponusun_like_kerotar, "ponusun")}
+               "kerotar": (KEROTAR_SIZES, kerotar_config, ponusun_like_kerotar, "ponusun"),
+               "pirisun": (PIRISUN_SIZES, pirisun_config, kerotar_like_pirisun, "kerotar")}
 
 
 def ponusun_arm(args) -> dict:
-    """Prompt and single-token throughput of Ponusun (or Zosurax, Kerotar: `--model`) and of the closest earlier
-    architecture (LFM2; for Kerotar, Ponusun) at equal size, random
+    """Prompt and single-token throughput of Ponusun (or Zosurax, Kerotar, Pirisun: `--model`) and of the closest earlier
+    architecture (LFM2; for Kerotar, Ponusun; for Pirisun, Kerotar) at equal size, random
     weights, bfloat16: one prompt of --prefill-tokens tokens in one step (median of 5), then --steps single-token
     steps of --batch sequences replayed from CUDA graphs (prompts of 512..2,048 tokens)."""
     import numpy as np
@@ -510,12 +565,12 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="with --only prefill: the prompt's length (the headline line always uses 2,048)")
-    ap.add_argument("--model", default="1.2b", choices=["1.2b", "ponusun", "zosurax", "kerotar"] + sorted(SECONDARY),
+    ap.add_argument("--model", default="1.2b", choices=["1.2b", "ponusun", "zosurax", "kerotar", "pirisun"] + sorted(SECONDARY),
                     help="1.2b: the headline benchmark; 2.6b, 350m: the secondary workloads (decode only); ponusun, zosurax, "
-                         "kerotar: that architecture beside the closest earlier one at equal size, prompt and single-token steps")
-    ap.add_argument("--size", default="", choices=[""] + sorted(PONUSUN_SIZES), help="with --model ponusun, zosurax or kerotar: one size only")
-    ap.add_argument("--arch", default="", choices=["", "ponusun", "zosurax", "kerotar", "lfm2"],
-                    help="with --model ponusun, zosurax or kerotar: one architecture of the two only")
+                         "kerotar, pirisun: that architecture beside the closest earlier one at equal size, prompt and single-token steps")
+    ap.add_argument("--size", default="", choices=[""] + sorted(PONUSUN_SIZES), help="with --model ponusun, zosurax, kerotar or pirisun: one size only")
+    ap.add_argument("--arch", default="", choices=["", "ponusun", "zosurax", "kerotar", "pirisun", "lfm2"],
+                    help="with --model ponusun, zosurax, kerotar or pirisun: one architecture of the two only")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
     if args.impl == "reference":

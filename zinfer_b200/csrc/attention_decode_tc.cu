@@ -180,6 +180,7 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
   // The softmax runs on base 2: scores are scaled by scale * log2(e) and the exponentials are ex2.approx
   // (one instruction where expf is eight); the maxima go back to base e when they leave the loop.
   const float scale2 = scale * 1.4426950408889634f;
+  const float cap2 = softcap * 1.4426950408889634f, scale_cap = softcap > 0.f ? scale / softcap : 0.f;
   const bool biased = bias_r1 != nullptr;
   float r1_2[2] = {0.f, 0.f}, r2[2] = {0.f, 0.f};     // row g = head g of the group, row g + 8 = head g + 8
   if (biased) {
@@ -238,7 +239,7 @@ __global__ void __launch_bounds__(DT_WARPS * 32)
       for (int i = 0; i < 4; ++i) {
         const int kp = kb + 8 * j + 2 * c + (i & 1);
         float sc = s[j][i] * scale2;
-        if (softcap > 0.f) sc = softcap * tanhf(s[j][i] * scale / softcap) * 1.4426950408889634f;
+        if (softcap > 0.f) sc = cap2 * fast_tanh(s[j][i] * scale_cap);
         if (biased) sc -= r1_2[i >> 1] * log1pf(r2[i >> 1] * (float)max(L - 1 - kp, 0));
         if (edge_tile) {
           const bool vis = (kp >= c0 || kp < keep_here) && kp < c1;

@@ -204,6 +204,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
     }
 
     // scale, mask, online softmax; each row's 64 scores sit in the 4 lanes of a quad
+    const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
     float m_new[2] = {m_run[0], m_run[1]};
 #pragma unroll
     for (int j = 0; j < 8; ++j)
@@ -213,7 +214,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
         const int kp = kb + 8 * j + 2 * c + (i & 1);
         const bool vis = row_ok[h] && (kp >= row_lo[h] || kp < keep) && kp < row_hi[h];
         float sc = s[j][i] * scale;
-        if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);     // capped scores
+        if (softcap > 0.f) sc = softcap * fast_tanh(sc * inv_cap);     // capped scores
         if (biased && vis) sc -= r1[h] * log1pf(r2[h] * (float)(row_hi[h] - 1 - kp));
         s[j][i] = vis ? sc : -INFINITY;
         m_new[h] = fmaxf(m_new[h], s[j][i]);

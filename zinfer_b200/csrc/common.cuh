@@ -51,6 +51,12 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return t;
 }
 
+// tanh(x) = 1 - 2 / (1 + e^{2x}) on the fast exponential and division: absolute error below 1e-6, exact limits
+// for large |x| (e^{2x} overflows to infinity, whose reciprocal is 0).  For score caps in the bfloat16 attention kernels.
+__device__ __forceinline__ float fast_tanh(float x) {
+  return 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * x));
+}
+
 static inline int ceil_div_i(int a, int b) { return (a + b - 1) / b; }
 
 // ------------------------------------------------------------------------------ dependent launches

@@ -308,6 +308,59 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
   }
 }
 
+// The same with 16-byte loads and the row kept in registers (dim a multiple of 4, at most 16 values per thread, aligned
+// rows): one pass over memory.  The sums are added per thread over its float4s in order, then over the block.
+template <typename TO>
+__global__ void layernorm_vec4_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+                                      const float* __restrict__ b, TO* __restrict__ y, int dim, float eps) {
+  __shared__ float scratch[32];
+  zk_let_next_start();
+  zk_wait_prior();
+  const int r = blockIdx.x;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * dim);
+  const int n4 = dim >> 2;
+  float4 v[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int d = threadIdx.x + i * blockDim.x;
+    v[i] = d < n4 ? xr[d] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  const float mean = block_sum(sum, scratch) / (float)dim;
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if ((int)(threadIdx.x + i * blockDim.x) >= n4) continue;
+    v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+    ss = fmaf(v[i].x, v[i].x, ss);
+    ss = fmaf(v[i].y, v[i].y, ss);
+    ss = fmaf(v[i].z, v[i].z, ss);
+    ss = fmaf(v[i].w, v[i].w, ss);
+  }
+  const float scale = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dim + eps);
+  TO* yr = y + (size_t)r * dim;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int d = threadIdx.x + i * blockDim.x;
+    if (d >= n4) continue;
+    const float4 wv = reinterpret_cast<const float4*>(w)[d];
+    const float4 bv = b ? reinterpret_cast<const float4*>(b)[d] : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float o0 = (v[i].x * scale) * wv.x + bv.x, o1 = (v[i].y * scale) * wv.y + bv.y;
+    const float o2 = (v[i].z * scale) * wv.z + bv.z, o3 = (v[i].w * scale) * wv.w + bv.w;
+    if constexpr (sizeof(TO) == 4) {
+      reinterpret_cast<float4*>(yr)[d] = make_float4(o0, o1, o2, o3);
+    } else {
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(o0, o1), hi = __floats2bfloat162_rn(o2, o3);
+      uint2 packed;
+      packed.x = *reinterpret_cast<const unsigned*>(&lo);
+      packed.y = *reinterpret_cast<const unsigned*>(&hi);
+      reinterpret_cast<uint2*>(yr)[d] = packed;
+    }
+  }
+}
+
 // A gate per value: rows[t, h, j] *= sigmoid(gate[t * ld_gate + h * valid + j]) for j < valid, in place; a head's row is
 // `width` values of which the first `valid` are gated (the rest is padding and left alone).  gate float32.
 template <typename T>
@@ -902,6 +955,14 @@ int zk_layernorm(const float* x, const int* rows, const float* w, const float* b
   if (dim <= 0 || !w) return ZK_EINVAL;
   int threads = 32;
   while (threads < 256 && threads * 4 < dim) threads <<= 1;
+  const bool aligned = (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(b) |
+                        reinterpret_cast<uintptr_t>(y)) % 16 == 0;
+  if (dim % 4 == 0 && dim <= 16 * threads && aligned && (out_dtype == ZK_F32 || out_dtype == ZK_BF16)) {
+    while (threads > 32 && threads * 4 >= 2 * dim) threads >>= 1;   // no idle warps for short rows
+    if (out_dtype == ZK_F32)
+      return zk_launch_dependent(layernorm_vec4_kernel<float>, dim3(n_out), dim3(threads), 0, stream, x, rows, w, b, (float*)y, dim, eps);
+    return zk_launch_dependent(layernorm_vec4_kernel<bf16>, dim3(n_out), dim3(threads), 0, stream, x, rows, w, b, (bf16*)y, dim, eps);
+  }
   if (out_dtype == ZK_F32)
     return zk_launch_dependent(layernorm_kernel<float>, dim3(n_out), dim3(threads), 0, stream, x, rows, w, b, (float*)y, dim, eps);
   if (out_dtype == ZK_BF16)
