@@ -273,7 +273,7 @@ def plain_latent(x, t, H, d, p, e, r, scale, base, eps=2e-6):
 @pytest.mark.parametrize("D,H,d,p,e,r,scale,base,page", [
     (48, 3, 8, 4, 10, 24, 0.5, 50.0, 16), (64, 2, 16, 8, 16, 32, 0.4, 1e4, 16), (128, 4, 32, 32, 64, 64, 0.25, 1e4, 64),
     (128, 2, 64, 16, 32, 128, 0.2, 1e3, 64), (38, 3, 6, 6, 5, 18, 0.5, 40.0, 16), (128, 20, 16, 16, 16, 48, 0.3, 1e5, 64),
-    (64, 1, 4, 2, 4, 8, 0.8, 20.0, 16)])
+    (64, 1, 4, 2, 4, 8, 0.8, 20.0, 16), (256, 2, 64, 32, 128, 96, 0.2, 1e4, 64)])
 def test_latent_attention_with_sink_and_value_gate(k, dtype, D, H, d, p, e, r, scale, base, page):
     """Unequal sequences, a prompt step (keys and values expanded) then single tokens (queries carried into the
     latent's space): both forms must agree with the plain function, the sink in either one's denominator."""
