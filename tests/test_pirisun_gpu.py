@@ -19,7 +19,7 @@ import pirisun_helpers as H
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-PAGE = {"pc": 64, "pf": 64}
+PAGE = {"pc": 64, "pf": 64, "pe": 64}      # "pe": heads of 10 / 7 values, padded up to the tensor-core kernels' 64 in bfloat16
 
 
 @pytest.fixture(scope="module")

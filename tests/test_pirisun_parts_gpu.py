@@ -149,10 +149,10 @@ def capped_tensors(D, H, G, d, e, dtype, seed):
             "v": rnd((G * e, D), seed + 2, dtype, D ** -0.5), "o": rnd((D, H * e), seed + 3, dtype, (H * e) ** -0.5)}
 
 
-def make_capped(D, H, G, d, e, scale, cap, q_temp, t, dtype):
+def make_capped(D, H, G, d, e, scale, cap, q_temp, t, dtype, pad=False):
     from zinfer_b200.parts import GqaAttention
-    return load(GqaAttention(D, H, G, d, "q", "k", "v", "o", scale=scale, value_dim=e, softcap=cap, query_temperature=q_temp),
-                t, dtype)
+    return load(GqaAttention(D, H, G, d, "q", "k", "v", "o", scale=scale, value_dim=e, softcap=cap, query_temperature=q_temp,
+                             pad_heads=pad), t, dtype)
 
 
 def plain_capped(x, t, H, G, d, e, scale, cap, q_temp):
@@ -169,13 +169,18 @@ def plain_capped(x, t, H, G, d, e, scale, cap, q_temp):
     (48, 4, 2, 16, 12, 0.6, 2.0, (0.4, 7), 16), (64, 6, 6, 8, 16, 0.7, None, None, 16), (38, 5, 1, 10, 7, 0.6, 4.0, (0.25, 3), 16),
     (128, 8, 2, 64, 64, 0.25, 3.0, (0.3, 16), 64), (128, 4, 4, 64, 64, 0.2, 50.0, None, 64), (128, 2, 1, 128, 128, 0.15, 2.5, (1.0, 50), 64),
     (64, 2, 1, 64, 128, 0.2, 3.0, (0.3, 128), 64), (32, 1, 1, 4, 6, 1.0, 1.0, (0.2, 1), 16), (128, 8, 2, 64, 64, 0.25, None, (0.5, 10), 64)])
-def test_capped_attention_alone(k, dtype, D, H, G, d, e, scale, cap, q_temp, page):
+@pytest.mark.parametrize("pad", [False, True])
+def test_capped_attention_alone(k, dtype, D, H, G, d, e, scale, cap, q_temp, page, pad):
     """Three unequal sequences: a prompt step then single tokens, over several periods of the temperature and several
-    pages; caps low enough to bend most scores.  The shapes include those of the two mma.sync kernels."""
+    pages; caps low enough to bend most scores.  The shapes include those of the two mma.sync kernels; with `pad`, heads
+    of other widths are padded up to them in a bfloat16 run (pages of 64 tokens, which those kernels want)."""
     t = capped_tensors(D, H, G, d, e, dtype, 40)
-    mixer = make_capped(D, H, G, d, e, scale, cap, q_temp, t, dtype)
+    mixer = make_capped(D, H, G, d, e, scale, cap, q_temp, t, dtype, pad)
+    padded = pad and dtype == torch.bfloat16 and not (d == e and d in (64, 128))
+    assert (mixer.run_head_dim, mixer.run_value_dim) == ((64, 64) if padded and max(d, e) <= 64 else (128, 128) if padded else (d, e))
+    assert mixer.kv_request().head_dim == mixer.run_head_dim and mixer.kv_request().v_dim == mixer.run_value_dim
     xs = [rnd((n, D), 50 + b, dtype, 1.5) for b, n in enumerate((150, 40, 9))]
-    outs = run_mixer(k, mixer, dtype, xs, [130, 17, 1], page=page)
+    outs = run_mixer(k, mixer, dtype, xs, [130, 17, 1], page=64 if pad else page)
     for b, x in enumerate(xs):
         close(outs[b], plain_capped(x, t, H, G, d, e, scale, cap, q_temp), dtype, f"sequence {b}")
 

@@ -35,7 +35,7 @@ def build_pirisun(cfg: PirisunConfig) -> Model:
         else:
             l, r = L.left, L.right
             left = GqaAttention(D, l.heads, l.kv_heads, l.dim, a + "left.q", a + "left.k", a + "left.v", a + "left.o",
-                                norm_eps=eps, scale=l.scale, value_dim=l.vdim, softcap=l.softcap or None,
+                                norm_eps=eps, scale=l.scale, value_dim=l.vdim, softcap=l.softcap or None, pad_heads=True,
                                 query_temperature=(l.q_temp_coef, l.q_temp_every) if l.q_temp_every else None)
             position = RotaryEncoding(r.dim, r.rot_base, n_rot=r.rot_dims) if r.rot_dims else None
             right = Retention(D, r.heads, r.dim, r.vdim, r.decay, a + "right.q", a + "right.k", a + "right.v", a + "right.g",

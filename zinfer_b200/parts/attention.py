@@ -25,6 +25,10 @@ one more term of head h's softmax denominator, with no key and no value, and is 
 `query_temperature` = (coef, every): the query at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)
 (positions enter through that factor alone when there is no position encoding).  `softcap`: a scaled score s becomes
 softcap * tanh(s / softcap) before the softmax.
+`pad_heads`: in a bfloat16 run, heads whose keys and values are not both 64 or both 128 wide (and at most 128) are
+padded at load to the next of those widths, with zero rows in W_q, W_k and W_v and zero columns in W_o, so that the
+tensor-core kernels take them; a padded entry adds nothing to a score and meets a zero column of W_o, the cache holds
+the padded rows.  Only without q/k norms (a norm would count the padding).
 
 How the kernels are launched is decided here, not by the engine: the table of query tiles of a
 step, and for single-token steps the cut of a sequence's keys into chunks that separate blocks
@@ -99,7 +103,7 @@ class GqaAttention(Mixer):
                  qk_norm_span: str = "head", distance_bias: Optional[tuple[str, str]] = None, own_kv: bool = True,
                  unit_norm_after_rotation: bool = False, talk_name: Optional[str] = None, keep_first: int = 0,
                  sink_name: Optional[str] = None, query_temperature: Optional[tuple[float, int]] = None,
-                 softcap: Optional[float] = None):
+                 softcap: Optional[float] = None, pad_heads: bool = False):
         """split_keys: keys per chunk of single-token attention, a multiple of 64 (0 = chosen per
         step from the batch and the GPU's size)."""
         if n_heads % n_kv_heads:
@@ -126,6 +130,10 @@ class GqaAttention(Mixer):
         if softcap is not None and (not softcap > 0 or talk_name is not None):
             raise ValueError("attention: a score cap must be positive and does not go with weights mixed across heads")
         self.softcap = 0.0 if softcap is None else float(softcap)
+        if pad_heads and (q_norm_name or k_norm_name or unit_norm_after_rotation or not own_kv or qk_norm_span == "all"):
+            raise ValueError("attention: padded heads go with key/value weights of the mixer's own and no q/k norms")
+        self.pad_heads = bool(pad_heads)
+        self.run_head_dim, self.run_value_dim = head_dim, self.value_dim      # the widths the kernels see (load may pad)
         if self.span_prepare and qk_norm_span == "head" and (q_norm_name or k_norm_name):
             raise ValueError("attention: per-head norms go with key/value weights of the mixer's own")
         if talk_name is not None and distance_bias is not None:
@@ -180,11 +188,30 @@ class GqaAttention(Mixer):
         return specs
 
     def load(self, weights, dtype, device):
-        if self.own_kv:
+        self.run_head_dim, self.run_value_dim = self.head_dim, self.value_dim
+        hd, vd = self.head_dim, self.value_dim
+        if (self.pad_heads and dtype == torch.bfloat16 and max(hd, vd) <= 128 and not (hd == vd and hd in (64, 128))
+                and (self.position is None or hasattr(self.position, "inv_freq_host"))):
+            P = 64 if max(hd, vd) <= 64 else 128
+            D = self.hidden
+
+            def rows(w, heads, width):                        # [heads * width, D] -> [heads * P, D], zero rows behind
+                out = torch.zeros((heads, P, D), dtype=w.dtype, device=w.device)
+                out[:, :width] = w.reshape(heads, width, D)
+                return out.reshape(heads * P, D)
+
+            w_o = torch.zeros((D, self.n_heads, P), dtype=weights[self.out_name].dtype, device=weights[self.out_name].device)
+            w_o[:, :, :vd] = weights[self.out_name].reshape(D, self.n_heads, vd)
+            self.w_qkv = torch.cat([rows(weights[self.q_name], self.n_heads, hd), rows(weights[self.k_name], self.n_kv, hd),
+                                    rows(weights[self.v_name], self.n_kv, vd)], dim=0).contiguous()
+            self.w_out = w_o.reshape(D, self.n_heads * P).contiguous()
+            self.run_head_dim = self.run_value_dim = P
+        elif self.own_kv:
             self.w_qkv = torch.cat([weights[self.q_name], weights[self.k_name], weights[self.v_name]], dim=0).contiguous()
+            self.w_out = weights[self.out_name]
         else:
             self.w_qkv = weights[self.q_name]
-        self.w_out = weights[self.out_name]
+            self.w_out = weights[self.out_name]
         self.q_norm = weights[self.q_norm_name] if self.q_norm_name else None
         self.k_norm = weights[self.k_norm_name] if self.k_norm_name and self.own_kv else None
         if self.distance_bias is not None:
@@ -194,8 +221,8 @@ class GqaAttention(Mixer):
         self._sm_count = kernels.sm_count(device) if torch.device(device).type == "cuda" else 0
 
     def kv_request(self):
-        return KVRequest(self.n_kv, self.head_dim, self.window,
-                         None if self.value_dim == self.head_dim else self.value_dim, keep_first=self.keep_first)
+        hd, vd = self.run_head_dim, self.run_value_dim        # as load left them: padded in a bfloat16 run with `pad_heads`
+        return KVRequest(self.n_kv, hd, self.window, None if vd == hd else vd, keep_first=self.keep_first)
 
     def check(self, dtype, page_size):
         most = kernels.attn_max_head_dim()
@@ -212,6 +239,7 @@ class GqaAttention(Mixer):
 
     def forward(self, ctx, call, xn, out, accumulate):
         kv = call.kv
+        hd, vd = self.run_head_dim, self.run_value_dim
         if not self.own_kv and call.writes_kv:
             raise ValueError("attention: a mixer without key and value weights must read another call's cache")
         # a call that reads another call's cache needs its queries only (the stacked rows start with q)
@@ -220,19 +248,19 @@ class GqaAttention(Mixer):
         rot = self.position.rotary() if self.position is not None else None
         fused = self.position is None or rot is not None
         common = dict(tok_seq=ctx.tok_seq, tok_pos=ctx.tok_pos, seq_slot=ctx.seq_slot, page_table=kv.page_table,
-                      n_heads=self.n_heads, n_kv=self.n_kv, head_dim=self.head_dim, eps=self.eps, status=ctx.status)
+                      n_heads=self.n_heads, n_kv=self.n_kv, head_dim=hd, eps=self.eps, status=ctx.status)
         if self.span_prepare:
             if self.position is not None and rot is None:
                 raise ValueError("attention: norms over the whole projection take a rotation table, no other encoding")
             if rot is not None and rot.interleaved:
                 raise ValueError("attention: norms over the whole projection take the half-split pairing only")
-            q = kernels.qk_prepare_span(qkv, kv.k, kv.v, self.q_norm, self.k_norm, value_dim=self.value_dim,
+            q = kernels.qk_prepare_span(qkv, kv.k, kv.v, self.q_norm, self.k_norm, value_dim=vd,
                                         write_kv=call.writes_kv, inv_freq=rot.inv_freq if rot else None,
                                         n_rot=rot.n_rot if rot else 0, **common)
         elif fused:
             q = kernels.qk_prepare(qkv, kv.k, kv.v, self.q_norm, self.k_norm, rot.inv_freq if rot else None,
                                    n_rot=rot.n_rot if rot else 0, interleaved=rot.interleaved if rot else False,
-                                   write_kv=call.writes_kv, value_dim=self.value_dim,
+                                   write_kv=call.writes_kv, value_dim=vd,
                                    unit_norm_after=self.unit_norm_after, query_temperature=self.query_temperature, **common)
         else:
             # A position encoding that is not a rotation table runs between the norm and the
@@ -245,8 +273,8 @@ class GqaAttention(Mixer):
             self.position.apply(ctx, normed[:, :self.q_dim], normed[:, self.q_dim:self.q_dim + self.kv_dim])
             q = kernels.qk_prepare(normed, kv.k, kv.v, None, None, None, n_rot=0, interleaved=False,
                                    write_kv=call.writes_kv, unit_norm_after=self.unit_norm_after, **common)
-        kind, tile_tokens = kernels.attention_plan(q.dtype, self.n_heads, self.n_kv, self.head_dim, kv.page_size,
-                                                   ctx.is_decode, self.window, self.value_dim,
+        kind, tile_tokens = kernels.attention_plan(q.dtype, self.n_heads, self.n_kv, hd, kv.page_size,
+                                                   ctx.is_decode, self.window, vd,
                                                    self.distance_bias is not None, self.talk_name is not None,
                                                    kept_or_sink=self.keep_first > 0 or self.sink is not None,
                                                    capped=self.softcap > 0)
@@ -254,9 +282,9 @@ class GqaAttention(Mixer):
         num_splits, split_keys = (key_chunks(ctx.n_seqs, self.n_kv, ctx.max_kv_len, self._sm_count, self.split_keys)
                                   if ctx.is_decode else (1, 0))
         att = kernels.attention(q, kv.k, kv.v, tile_seq, tile_q0, ctx.cu_q, ctx.seq_start, ctx.seq_slot,
-                                kv.page_table, self.n_heads, self.n_kv, self.head_dim, self.scale, self.window,
+                                kv.page_table, self.n_heads, self.n_kv, hd, self.scale, self.window,
                                 num_splits, split_keys, single_token=ctx.is_decode, kind=kind,
-                                value_dim=self.value_dim,
+                                value_dim=vd,
                                 bias=(self.bias_r1, self.bias_r2) if self.distance_bias is not None else None,
                                 talk=self.talk, keep_first=self.keep_first, sink=self.sink, softcap=self.softcap)
         linear(att, self.w_out, out=out, accumulate=accumulate)
