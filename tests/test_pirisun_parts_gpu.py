@@ -86,6 +86,14 @@ def test_sum_of_a_share_of_normalised_rows(k, scale):
     close(got, f64(x) + scale * P.rms(f64(m), 1e-6) * f64(w), torch.float32, "share of a norm")
 
 
+@pytest.mark.parametrize("dim", [38, 200, 2048, 5000])
+def test_sum_of_two_normalised_rows(k, dim):
+    a, b, x = rnd((7, dim), 1, torch.float32, 2.0), rnd((7, dim), 2, torch.float32, 0.1), rnd((7, dim), 3, torch.float32)
+    wa, wb = 1.0 + rnd((dim,), 4, torch.float32, 0.2), 1.0 + rnd((dim,), 5, torch.float32, 0.2)
+    got = k.rmsnorm_pair_add(a.cuda(), b.cuda(), wa.cuda(), wb.cuda(), 1e-6, x.clone().cuda(), 0.5)
+    close(got, f64(x) + 0.5 * (P.rms(f64(a), 1e-6) * f64(wa) + P.rms(f64(b), 1e-6) * f64(wb)), torch.float32, "pair of norms")
+
+
 # ------------------------------------------------------------------------------- retention
 
 def retention_tensors(D, H, d, e, dtype, seed):

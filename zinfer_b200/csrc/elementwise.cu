@@ -425,6 +425,51 @@ __global__ void unit_norm_gate_kernel(const float* __restrict__ o, const float* 
   }
 }
 
+// x[r, :] += share * ((a[r, :] * rsqrt(mean(a^2) + eps)) * wa + (b[r, :] * rsqrt(mean(b^2) + eps)) * wb): the results of two
+// mixers that ran side by side, each RMS-normalised with a weight of its own, summed into the residual rows in one pass
+// (x is read and written once).  Float32; one block per row; both rows stay in registers when they fit (8 values per
+// thread each), else they are read twice.
+__global__ void rmsnorm_pair_add_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ wa,
+                                        const float* __restrict__ wb, float* __restrict__ x, int dim, float eps, float share) {
+  __shared__ float scratch[32];
+  zk_let_next_start();
+  zk_wait_prior();
+  const int r = blockIdx.x;
+  const float* ar = a + (size_t)r * dim;
+  const float* br = b + (size_t)r * dim;
+  float* xr = x + (size_t)r * dim;
+  float ka[8], kb[8];
+  const bool fits = dim <= 8 * (int)blockDim.x;
+  float sa = 0.f, sb = 0.f;
+  if (fits) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int d = threadIdx.x + i * blockDim.x;
+      ka[i] = d < dim ? ar[d] : 0.f;
+      kb[i] = d < dim ? br[d] : 0.f;
+      sa = fmaf(ka[i], ka[i], sa);
+      sb = fmaf(kb[i], kb[i], sb);
+    }
+  } else {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+      sa = fmaf(ar[d], ar[d], sa);
+      sb = fmaf(br[d], br[d], sb);
+    }
+  }
+  sa = block_sum(sa, scratch);
+  sb = block_sum(sb, scratch);
+  const float ra = 1.0f / sqrtf(sa / (float)dim + eps), rb = 1.0f / sqrtf(sb / (float)dim + eps);
+  if (fits) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int d = threadIdx.x + i * blockDim.x;
+      if (d < dim) xr[d] += share * ((ka[i] * ra) * wa[d] + (kb[i] * rb) * wb[d]);
+    }
+  } else {
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) xr[d] += share * ((ar[d] * ra) * wa[d] + (br[d] * rb) * wb[d]);
+  }
+}
+
 // Activations of a plain (ungated) feed-forward, float32 arithmetic:
 // 0 = gelu with erf: 0.5 z (1 + erf(z / sqrt 2)); 1 = gelu with tanh:
 // 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 2 = silu; 3 = relu; 4 = the square of relu.
@@ -831,6 +876,15 @@ int zk_rmsnorm_add(const float* m, const float* w, float* x, int n, int dim, flo
     return zk_launch_dependent(rmsnorm_add_vec4_kernel, dim3(n), dim3(threads), 0, stream, m, w, x, dim, eps, out_scale);
   }
   return zk_launch_dependent(rmsnorm_add_kernel, dim3(n), dim3(threads), 0, stream, m, w, x, dim, eps, out_scale);
+}
+
+int zk_rmsnorm_pair_add(const float* a, const float* b, const float* wa, const float* wb, float* x, int n, int dim, float eps,
+                        float share, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (dim <= 0) return ZK_EINVAL;
+  int threads = 32;
+  while (threads < 256 && threads * 8 < dim) threads <<= 1;
+  return zk_launch_dependent(rmsnorm_pair_add_kernel, dim3(n), dim3(threads), 0, stream, a, b, wa, wb, x, dim, eps, share);
 }
 
 int zk_activation(const void* in, void* out, long long total, int kind, int dtype, cudaStream_t stream) {

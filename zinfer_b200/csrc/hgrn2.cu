@@ -44,26 +44,35 @@ __global__ void hgrn2_gates_kernel(float* __restrict__ qfv, int ld, const float*
 // What a retention layer does to its projections before the recurrence, in place on the float32 rows [q (H*d) | k (H*d)
 // | ...]: the first n_rot entries of every q and k head are rotated by the token's position (entry i pairs with entry
 // i + n_rot/2, angle = float(pos) * inv_freq[i]; inv_freq null = no rotation), then k is multiplied by key_scale.
-__global__ void retention_prepare_kernel(float* __restrict__ qk, int ld, const float* __restrict__ inv_freq, int n_rot,
-                                         float key_scale, const int* __restrict__ tok_pos, int n, int H, int d) {
+// Block (t, y) takes `slots_per_block` of token t's 2H heads: the cosines and sines of the position are computed once per
+// block (with many tokens one block serves all 2H heads; with few, the heads are spread over more blocks).
+__global__ void __launch_bounds__(256)
+    retention_prepare_kernel(float* __restrict__ qk, int ld, const float* __restrict__ inv_freq, int n_rot, float key_scale,
+                             const int* __restrict__ tok_pos, int H, int d, int slots_per_block) {
+  __shared__ float cs[HG_MAX_D / 2], sn[HG_MAX_D / 2];
   zk_let_next_start();
   zk_wait_prior();
+  const int t = blockIdx.x;
   const int half = inv_freq ? n_rot >> 1 : 0;
+  const float pos = (float)tok_pos[t];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float ang = pos * inv_freq[i];
+    cs[i] = cosf(ang);
+    sn[i] = sinf(ang);
+  }
+  __syncthreads();
   const int per_head = d - half;                      // work items of a head: its pairs, then its unrotated entries
-  const size_t total = (size_t)n * 2 * H * per_head;
-  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-    const size_t th = idx / per_head;
-    const int i = (int)(idx - th * per_head);
-    const size_t t = th / (2 * H);
-    const int s = (int)(th - t * 2 * H);              // head slot: the H query heads, then the H key heads
-    float* head = qk + t * ld + (size_t)s * d;
+  float* row = qk + (size_t)t * ld;
+  const int s0 = blockIdx.y * slots_per_block, s_here = min(2 * H, s0 + slots_per_block) - s0;
+  for (int idx = threadIdx.x; idx < s_here * per_head; idx += blockDim.x) {
+    const int s = s0 + idx / per_head, i = idx % per_head;      // head slot: the H query heads, then the H key heads
+    float* head = row + (size_t)s * d;
     const float mul = s >= H ? key_scale : 1.0f;
     if (i < half) {
-      const float ang = (float)tok_pos[t] * inv_freq[i];
-      const float c = cosf(ang), sn = sinf(ang);
+      const float c = cs[i], sv = sn[i];
       const float u = head[i], v = head[i + half];
-      head[i] = (u * c - v * sn) * mul;
-      head[i + half] = (v * c + u * sn) * mul;
+      head[i] = (u * c - v * sv) * mul;
+      head[i + half] = (v * c + u * sv) * mul;
     } else if (s >= H) {
       head[i + half] *= mul;
     }
@@ -255,12 +264,9 @@ int zk_retention_scan(float* qkv, int ld, const float* decay, const float* inv_f
   if (H <= 0 || d <= 0 || e <= 0 || d > HG_MAX_D || ld < 2 * H * d + H * e || !decay || !tok_pos) return ZK_EINVAL;
   if (inv_freq && (n_rot <= 0 || (n_rot & 1) || n_rot > d)) return ZK_EINVAL;
   if (inv_freq || key_scale != 1.0f) {
-    const size_t total = (size_t)n * 2 * H * (d - (inv_freq ? n_rot / 2 : 0));
-    const int threads = 256;
-    const size_t want = (total + threads - 1) / threads;
-    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
-    const int rc = zk_launch_dependent(retention_prepare_kernel, dim3(blocks), dim3(threads), 0, stream, qkv, ld, inv_freq, n_rot,
-                                       key_scale, tok_pos, n, H, d);
+    const int per = n >= 256 ? 2 * H : (2 * H + 7) / 8;       // head slots a block takes
+    const int rc = zk_launch_dependent(retention_prepare_kernel, dim3(n, (2 * H + per - 1) / per), dim3(256), 0, stream, qkv, ld,
+                                       inv_freq, n_rot, key_scale, tok_pos, H, d, per);
     if (rc != 0) return rc;
   }
   dim3 grid(n_seqs, H, (e + 31) / 32);

@@ -29,6 +29,7 @@ _SIGNATURES = {
         "zk_silu_mul": "ppiiiip",
         "zk_fill_normal": "pllffip",
         "zk_rmsnorm_add": "pppiiffp",
+        "zk_rmsnorm_pair_add": "pppppiiffp",
         "zk_activation": "ppliip",
         "zk_cast_rows": "pplip",
         "zk_softcap": "plfp",
@@ -267,6 +268,19 @@ def rmsnorm_add(m: torch.Tensor, weight: torch.Tensor, eps: float, x: torch.Tens
     _check(_fn("elementwise", "zk_rmsnorm_add")(_ptr(m), _ptr(weight), _ptr(x), m.shape[0], m.shape[1], eps, float(scale),
                                                 _stream()),
            "rmsnorm_add")
+    return x
+
+
+def rmsnorm_pair_add(a: torch.Tensor, b: torch.Tensor, weight_a: torch.Tensor, weight_b: torch.Tensor, eps: float,
+                     x: torch.Tensor, share: float = 0.5) -> torch.Tensor:
+    """x += share * (RMSNorm(a) * weight_a + RMSNorm(b) * weight_b), row by row, all float32, in one pass over x."""
+    _need(a, "a", torch.float32, (None, None))
+    _need(b, "b", torch.float32, tuple(a.shape))
+    _need(x, "x", torch.float32, tuple(a.shape))
+    _need(weight_a, "weight_a", torch.float32, (a.shape[1],))
+    _need(weight_b, "weight_b", torch.float32, (a.shape[1],))
+    _check(_fn("elementwise", "zk_rmsnorm_pair_add")(_ptr(a), _ptr(b), _ptr(weight_a), _ptr(weight_b), _ptr(x), a.shape[0],
+                                                     a.shape[1], eps, float(share), _stream()), "rmsnorm_pair_add")
     return x
 
 

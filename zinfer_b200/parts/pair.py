@@ -5,7 +5,7 @@ with a weight of its own, and the pair's result is a fixed share of their sum (h
 
 The two mixers are any parts with the `Mixer` interface; at most one of them may ask for a growing cache and at most
 one for a per-sequence state (the call's storage is handed to both as it is, each takes what it asked for).  Norms and
-sums are float32 (`kernels.rmsnorm_add` with the share as its output scale, one launch per side)."""
+sums are float32, both norms and the sum into the rows one kernel (`kernels.rmsnorm_pair_add`)."""
 from __future__ import annotations
 
 import torch
@@ -59,10 +59,10 @@ class MixerPair(Mixer):
         rows = out.rows if hasattr(out, "rows") else out
         if not accumulate:
             rows.zero_()
-        for mixer, w in ((self.first, self.w_first), (self.second, self.w_second)):
-            m = torch.empty((h.shape[0], self.hidden), dtype=torch.float32, device=h.device)
-            mixer.forward(ctx, call, h, m, False)
-            kernels.rmsnorm_add(m, w, self.eps, rows, self.share)
+        both = torch.empty((2, h.shape[0], self.hidden), dtype=torch.float32, device=h.device)
+        self.first.forward(ctx, call, h, both[0], False)
+        self.second.forward(ctx, call, h, both[1], False)
+        kernels.rmsnorm_pair_add(both[0], both[1], self.w_first, self.w_second, self.eps, rows, self.share)
 
 
 MIXERS.register("mixer_pair", MixerPair)
