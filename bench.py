@@ -360,10 +360,10 @@ def pirisun_config(sz: dict) -> dict:
         if i % 2 == 0:
             kind = "parallel"
             mixer = {"left": {"heads": sz["heads"], "kv_heads": sz["kv"], "dim": sz["dim"], "vdim": sz["dim"], "scale": sz["dim"] ** -0.5,
-                              "softcap": 30.0, "q_temp": {"coef": 0.3, "every": 128}},
+                              "softcap": 50.0, "q_temp": {"coef": 0.1, "every": 256}},
                      "right": {"heads": sz["ret_heads"], "dim": sz["ret_dim"], "vdim": sz["width"] // sz["ret_heads"],
-                               "decay": [1.0 - 2.0 ** -(5 + h % 6) for h in range(sz["ret_heads"])],
-                               "rot": {"base": 1000000.0, "dims": sz["ret_dim"]}}}
+                               "decay": [1.0 - 1.0 / (24.0 * (h + 1)) for h in range(sz["ret_heads"])],
+                               "rot": {"base": 10000.0, "dims": sz["ret_dim"]}}}
         else:
             kind = "latent_attention"
             mixer = {"heads": sz["heads"], "dim": sz["lat_dim"], "rot_dim": sz["lat_rot"], "vdim": sz["lat_vdim"],

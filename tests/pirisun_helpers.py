@@ -71,14 +71,14 @@ CONFIGS = {
     "pc": {"architecture": "Pirisun", "vocab": 512, "width": 128, "norm": {"eps": 1e-5}, "logit_scale": 2.0,
            "loop": {"start": 1, "stop": 3, "times": 2},
            "layers": [_latent(4, 32, 32, 64, 64, 0.12, 10000.0, mlp=_moe(8, 2, 64, identity=2, shared=128)),
-                      _pair(_left(8, 2, 64, 64, 0.12, softcap=8.0, q_temp=(0.3, 16)), _right(4, 32, 32, (0.96, 0.98, 0.99, 0.999), rot=(300000.0, 32)),
+                      _pair(_left(8, 2, 64, 64, 0.12, softcap=8.0, q_temp=(0.35, 16)), _right(4, 32, 32, (0.96, 0.98, 0.99, 0.999), rot=(300000.0, 32)),
                             mlp=_moe(8, 3, 64, identity=1)),
                       _latent(2, 64, 16, 32, 128, 0.1, 1000.0),
                       _pair(_left(4, 4, 64, 64, 0.11, softcap=50.0), _right(2, 64, 64, (0.9, 0.99), rot=(500.0, 32)), mlp=_moe(3, 1, 128))]},
     # the same kernels as "pc" with every router output chosen, so that bfloat16 runs compare at every position
     "pf": {"architecture": "Pirisun", "vocab": 256, "width": 128, "norm": {"eps": 1e-5}, "logit_scale": 2.0,
            "loop": {"start": 0, "stop": 2, "times": 2},
-           "layers": [_pair(_left(8, 2, 64, 64, 0.12, softcap=6.0, q_temp=(0.3, 32)), _right(4, 32, 32, (0.96, 0.98, 0.99, 0.999), rot=(10000.0, 16)),
+           "layers": [_pair(_left(8, 2, 64, 64, 0.12, softcap=6.0, q_temp=(0.25, 32)), _right(4, 32, 32, (0.96, 0.98, 0.99, 0.999), rot=(10000.0, 16)),
                             mlp=_moe(3, 5, 64, identity=2, shared=64)),
                       _latent(4, 32, 32, 64, 64, 0.12, 10000.0, mlp=_moe(4, 4, 32)),
                       _pair(_left(2, 1, 128, 128, 0.09, softcap=20.0), _right(2, 64, 64, (0.9, 0.99)))]},

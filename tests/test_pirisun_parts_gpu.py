@@ -175,8 +175,8 @@ def plain_capped(x, t, H, G, d, e, scale, cap, q_temp):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("D,H,G,d,e,scale,cap,q_temp,page", [
     (48, 4, 2, 16, 12, 0.6, 2.0, (0.4, 7), 16), (64, 6, 6, 8, 16, 0.7, None, None, 16), (38, 5, 1, 10, 7, 0.6, 4.0, (0.25, 3), 16),
-    (128, 8, 2, 64, 64, 0.25, 3.0, (0.3, 16), 64), (128, 4, 4, 64, 64, 0.2, 50.0, None, 64), (128, 2, 1, 128, 128, 0.15, 2.5, (1.0, 50), 64),
-    (64, 2, 1, 64, 128, 0.2, 3.0, (0.3, 128), 64), (32, 1, 1, 4, 6, 1.0, 1.0, (0.2, 1), 16), (128, 8, 2, 64, 64, 0.25, None, (0.5, 10), 64)])
+    (128, 8, 2, 64, 64, 0.25, 3.0, (0.35, 16), 64), (128, 4, 4, 64, 64, 0.2, 50.0, None, 64), (128, 2, 1, 128, 128, 0.15, 2.5, (1.0, 50), 64),
+    (64, 2, 1, 64, 128, 0.2, 3.0, (0.35, 96), 64), (32, 1, 1, 4, 6, 1.0, 1.0, (0.2, 1), 16), (128, 8, 2, 64, 64, 0.25, None, (0.5, 10), 64)])
 @pytest.mark.parametrize("pad", [False, True])
 def test_capped_attention_alone(k, dtype, D, H, G, d, e, scale, cap, q_temp, page, pad):
     """Three unequal sequences: a prompt step then single tokens, over several periods of the temperature and several
@@ -218,7 +218,7 @@ def test_one_marked_key_decides_the_last_query(k, dtype, H, G, d, page, mark):
     t["k"][:, D // 2:] = 0.0
     t["v"][:, :D // 2] = 0.0
     t["q"] = t["k"].reshape(G, 1, d, D).expand(G, H // G, d, D).reshape(H * d, D).clone()
-    scale, cap, q_temp = 8.0 / d, 60.0, (0.3, 64)
+    scale, cap, q_temp = 8.0 / d, 60.0, (0.35, 64)
     mixer = make_capped(D, H, G, d, d, scale, cap, q_temp, t, dtype)
     x = rnd((T, D), 71, dtype)
     x[mark, :D // 2] *= 2.0                                    # a long key, so that its match with itself stands out
@@ -237,7 +237,7 @@ def test_one_marked_key_decides_the_last_query(k, dtype, H, G, d, page, mark):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("D,left,right", [(48, (4, 2, 16, 12, 0.3, 2.0, (0.4, 7)), (3, 8, 10, (0.9, 0.97, 0.995), (100.0, 4))),
-                                          (128, (8, 2, 64, 64, 0.12, 8.0, (0.3, 16)), (4, 32, 32, (0.96, 0.98, 0.99, 0.999), (3e5, 32)))])
+                                          (128, (8, 2, 64, 64, 0.12, 8.0, (0.35, 16)), (4, 32, 32, (0.96, 0.98, 0.99, 0.999), (3e5, 32)))])
 def test_mixer_pair(k, dtype, D, left, right):
     """Half the sum of the two normalised results; the attention side takes the call's cache and the recurrence its
     state, through prompt steps and single-token steps of unequal sequences."""
